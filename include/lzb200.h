@@ -1,0 +1,168 @@
+/*
+ * lzb200 - C ABI of the B200 forward pipe for Leela Zero networks.
+ *
+ * This is the boundary a host program binds to.  It stands where the
+ * reference engine reaches its GPU backend: a C++ ForwardPipe implementation
+ * (CUDAPipe, shipped beside this library) calls these functions the way
+ * OpenCLScheduler calls OpenCL_Network.  Plain pointers and sizes only; every
+ * function returns a status code; no exceptions cross the boundary.
+ *
+ * Threading: a pipe is immutable after lzb_pipe_finalize().  Each lzb_ctx owns
+ * a stream and private activation buffers, so different contexts may be
+ * driven from different host threads at the same time.  One context must not
+ * be used by two threads at once.
+ *
+ * There is no CPU fallback: every entry point that computes needs a CUDA
+ * device of compute capability 10.0 and fails with LZB_ERR_CUDA otherwise.
+ */
+#ifndef LZB200_H
+#define LZB200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LZB_OK 0
+#define LZB_ERR_ARG 1       /* bad argument, wrong call order, unsupported shape */
+#define LZB_ERR_CUDA 2      /* a CUDA runtime / driver call failed               */
+#define LZB_ERR_DEVICE_WAIT 3 /* a kernel gave up a bounded wait (see error text) */
+#define LZB_ERR_NOMEM 4
+
+/* Arithmetic of the residual tower. */
+#define LZB_FP32 0   /* fp32 storage, FFMA contraction                            */
+#define LZB_FP16 1   /* fp16 operands on tcgen05, fp32 accumulation               */
+#define LZB_BF16 2   /* bf16 operands on tcgen05, fp32 accumulation               */
+
+#define LZB_INPUT_PLANES 18
+#define LZB_SQ 361
+#define LZB_IN_FLOATS (18 * 361)   /* one position, as Network::gather_features makes it */
+#define LZB_POL_FLOATS (2 * 361)   /* policy head 1x1 conv planes                          */
+#define LZB_VAL_FLOATS 361         /* value head 1x1 conv plane                            */
+#define LZB_MOVES 362
+
+typedef struct lzb_pipe lzb_pipe;  /* weights of one network on one GPU      */
+typedef struct lzb_ctx lzb_ctx;    /* stream + activation buffers on a pipe  */
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* lzb_last_error(void);
+
+/* Number of CUDA devices visible.  Replaces the platform/device scan of
+ * OpenCL::OpenCL (src/OpenCL.cpp:708-858). */
+int lzb_device_count(int* count);
+
+/*
+ * Create a pipe on CUDA device `device` for a tower of `blocks` residual
+ * blocks with `channels` filters.  `precision` is LZB_FP32/FP16/BF16.
+ * Replaces OpenCL::initialize + OpenCL_Network construction
+ * (src/OpenCL.cpp:860-930, src/OpenCLScheduler.cpp:85-106); there is no
+ * tuner run, kernel shapes are fixed.
+ */
+int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks,
+                    int precision);
+void lzb_pipe_destroy(lzb_pipe* p);
+
+/*
+ * Upload one 3x3 convolution layer.  `layer` 0 is the input convolution
+ * (c_in = 18), layers 1..2*blocks are the tower (c_in = channels).
+ * U is the Winograd-transformed filter exactly as the engine hands it to a
+ * ForwardPipe: fp32 [36][c_in][channels] (src/Network.cpp:215,
+ * src/ForwardPipe.h:43).  bn_mean has the conv bias folded in and bn_invstd is
+ * 1/sqrt(var + 1e-5) (src/Network.cpp:151-157, 554-576).
+ * Replaces OpenCLScheduler::push_input_convolution / push_residual
+ * (src/OpenCLScheduler.cpp:157-210).
+ */
+int lzb_pipe_push_conv(lzb_pipe* p, int layer, const float* U, int c_in,
+                       const float* bn_mean, const float* bn_invstd);
+
+/*
+ * Upload the two 1x1 head convolutions: pol_w fp32 [2][channels], val_w fp32
+ * [1][channels] (biases are folded away by the engine).  Replaces
+ * OpenCLScheduler::push_convolve (src/OpenCLScheduler.cpp:212-221).
+ */
+int lzb_pipe_push_head_convs(lzb_pipe* p, const float* pol_w, const float* val_w);
+
+/*
+ * Optional: upload what Network keeps private for the heads
+ * (src/Network.h:166-183) so that lzb_ctx_forward_heads can finish the
+ * evaluation on the GPU.  Means have the 1x1 conv biases folded in and
+ * *_invstd are 1/sqrt(var + 1e-5).  ip_pol_w [362][722], ip1_val_w [256][361],
+ * ip2_val_w [256].
+ */
+int lzb_pipe_push_heads(lzb_pipe* p, const float* bn_pol_mean,
+                        const float* bn_pol_invstd, const float* ip_pol_w,
+                        const float* ip_pol_b, const float* bn_val_mean,
+                        const float* bn_val_invstd, const float* ip1_val_w,
+                        const float* ip1_val_b, const float* ip2_val_w,
+                        const float* ip2_val_b);
+
+/* Check that every layer arrived; after this the pipe is read-only. */
+int lzb_pipe_finalize(lzb_pipe* p);
+
+/*
+ * Create an execution context able to run up to `max_batch` positions per
+ * call.  Replaces the per-thread OpenCLContext with its buffers
+ * (src/OpenCL.h:64-84, src/OpenCL.cpp:156-202).
+ */
+int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch);
+void lzb_ctx_destroy(lzb_ctx* c);
+
+/*
+ * Evaluate n positions held in HOST memory.  in: [n][18][361] fp32; pol:
+ * [n][2][361]; val: [n][361] - the raw 1x1 head planes, exactly what
+ * ForwardPipe::forward returns per position (src/ForwardPipe.h:62-64).
+ * Copies in, runs the tower, copies out and returns when the results are in
+ * pol/val.  Replaces OpenCL_Network::forward (src/OpenCL.cpp:143-329).
+ */
+int lzb_ctx_forward(lzb_ctx* c, const float* in, int n, float* pol, float* val);
+
+/*
+ * Same computation with DEVICE pointers, enqueued on the context's stream
+ * without waiting; call lzb_ctx_sync to wait and collect the status.
+ */
+int lzb_ctx_forward_device(lzb_ctx* c, const float* in_dev, int n, float* pol_dev,
+                           float* val_dev);
+
+/*
+ * Host buffers in, finished evaluation out: policy [n][362] after softmax
+ * (temperature softmax_temp) and winrate [n] = (1 + tanh(v)) / 2, i.e. the
+ * values Network::get_output_internal computes on the CPU
+ * (src/Network.cpp:833-851), before the symmetry un-rotation.  Needs
+ * lzb_pipe_push_heads.
+ */
+int lzb_ctx_forward_heads(lzb_ctx* c, const float* in, int n, float softmax_temp,
+                          float* policy, float* winrate);
+int lzb_ctx_forward_heads_device(lzb_ctx* c, const float* in_dev, int n,
+                                 float softmax_temp, float* policy_dev,
+                                 float* winrate_dev);
+
+/* Wait for everything enqueued on the context; reports device-side errors. */
+int lzb_ctx_sync(lzb_ctx* c);
+
+/* The context's cudaStream_t, for callers that time or order work on it. */
+void* lzb_ctx_stream(lzb_ctx* c);
+
+/*
+ * Positions pushed through the tower together (the batch is cut into pieces
+ * of this size so that the transformed tiles stay in L2).  0 restores the
+ * default.
+ */
+int lzb_ctx_set_micro_batch(lzb_ctx* c, int positions);
+
+/* Kernel launches issued by this context since it was created. */
+long long lzb_ctx_launch_count(const lzb_ctx* c);
+
+/*
+ * Diagnostics for tests: run one 3x3 layer (input transform, contraction,
+ * output transform + batch-norm [+ residual] + ReLU) on n positions given as
+ * fp32 NCHW host arrays and return the fp32 NCHW result.  layer 0 takes
+ * [n][18][361]; other layers take [n][channels][361]; residual may be NULL.
+ */
+int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n,
+                       const float* residual, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

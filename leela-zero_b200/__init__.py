@@ -1,0 +1,209 @@
+"""Python binding of the lzb200 C ABI (``include/lzb200.h``).
+
+The arithmetic lives in ``liblzb200.so`` (hand-written sm_100a CUDA); this
+module only marshals numpy arrays through ctypes, the way a cgo/JNI stub would.
+There is no fallback: if the library is missing or no B200 is visible, calls
+raise.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "liblzb200.so")
+
+FP32, FP16, BF16 = 0, 1, 2
+PRECISIONS = {"fp32": FP32, "fp16": FP16, "bf16": BF16}
+IN_FLOATS, POL_FLOATS, VAL_FLOATS, MOVES = 18 * 361, 2 * 361, 361, 362
+
+# every symbol include/lzb200.h declares
+SYMBOLS = (
+    "lzb_last_error", "lzb_device_count", "lzb_pipe_create", "lzb_pipe_destroy",
+    "lzb_pipe_push_conv", "lzb_pipe_push_head_convs", "lzb_pipe_push_heads",
+    "lzb_pipe_finalize", "lzb_ctx_create", "lzb_ctx_destroy", "lzb_ctx_forward",
+    "lzb_ctx_forward_device", "lzb_ctx_forward_heads", "lzb_ctx_forward_heads_device",
+    "lzb_ctx_sync", "lzb_ctx_stream", "lzb_ctx_set_micro_batch", "lzb_ctx_launch_count",
+    "lzb_ctx_debug_conv",
+)
+
+_f32p = ctypes.POINTER(ctypes.c_float)
+_lib = None
+
+
+class LzbError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("lzb200 error %d: %s" % (code, text))
+        self.code = code
+
+
+def lib():
+    """Load liblzb200.so (raises if it was not built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError("%s is missing: run `python leela-zero_b200/build.py`" % LIB_PATH)
+        L = ctypes.CDLL(LIB_PATH)
+        L.lzb_last_error.restype = ctypes.c_char_p
+        L.lzb_ctx_stream.restype = ctypes.c_void_p
+        L.lzb_ctx_launch_count.restype = ctypes.c_longlong
+        vp = ctypes.c_void_p
+        L.lzb_pipe_create.argtypes = [ctypes.POINTER(vp)] + [ctypes.c_int] * 4
+        L.lzb_pipe_destroy.argtypes = [vp]
+        L.lzb_pipe_push_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
+        L.lzb_pipe_push_head_convs.argtypes = [vp, _f32p, _f32p]
+        L.lzb_pipe_push_heads.argtypes = [vp] + [_f32p] * 10
+        L.lzb_pipe_finalize.argtypes = [vp]
+        L.lzb_ctx_create.argtypes = [ctypes.POINTER(vp), vp, ctypes.c_int]
+        L.lzb_ctx_destroy.argtypes = [vp]
+        L.lzb_ctx_forward.argtypes = [vp, vp, ctypes.c_int, vp, vp]
+        L.lzb_ctx_forward_device.argtypes = [vp, vp, ctypes.c_int, vp, vp]
+        L.lzb_ctx_forward_heads.argtypes = [vp, vp, ctypes.c_int, ctypes.c_float, vp, vp]
+        L.lzb_ctx_forward_heads_device.argtypes = [vp, vp, ctypes.c_int, ctypes.c_float, vp, vp]
+        L.lzb_ctx_sync.argtypes = [vp]
+        L.lzb_ctx_stream.argtypes = [vp]
+        L.lzb_ctx_set_micro_batch.argtypes = [vp, ctypes.c_int]
+        L.lzb_ctx_launch_count.argtypes = [vp]
+        L.lzb_ctx_debug_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
+        _lib = L
+    return _lib
+
+
+def check(code):
+    if code != 0:
+        raise LzbError(code, lib().lzb_last_error().decode())
+
+
+def _ptr(a):
+    assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(_f32p)
+
+
+def device_count():
+    n = ctypes.c_int(0)
+    check(lib().lzb_device_count(ctypes.byref(n)))
+    return n.value
+
+
+class Pipe:
+    """A network resident on one GPU (``lzb_pipe``).
+
+    ``net`` is a dict with the arrays a ``ForwardPipe`` receives in
+    ``push_weights`` (src/ForwardPipe.h:40-54): ``U`` (list of fp32
+    ``[36][c_in][C]``), ``bn_mean``, ``bn_invstd`` (lists of ``[C]``),
+    ``pol_w`` ``[2][C]``, ``val_w`` ``[1][C]``, plus optionally ``heads``.
+    """
+
+    def __init__(self, net, precision="fp16", device=0, heads=True):
+        L = lib()
+        self.h = ctypes.c_void_p()
+        self.channels, self.blocks = net["channels"], net["blocks"]
+        self.precision = PRECISIONS[precision] if isinstance(precision, str) else precision
+        check(L.lzb_pipe_create(ctypes.byref(self.h), device, self.channels, self.blocks,
+                                self.precision))
+        for l, U in enumerate(net["U"]):
+            U = np.ascontiguousarray(U, np.float32)
+            check(L.lzb_pipe_push_conv(self.h, l, _ptr(U), U.shape[1],
+                                       _ptr(np.ascontiguousarray(net["bn_mean"][l], np.float32)),
+                                       _ptr(np.ascontiguousarray(net["bn_invstd"][l], np.float32))))
+        check(L.lzb_pipe_push_head_convs(self.h, _ptr(np.ascontiguousarray(net["pol_w"], np.float32)),
+                                         _ptr(np.ascontiguousarray(net["val_w"], np.float32))))
+        self.has_heads = bool(heads and "heads" in net)
+        if self.has_heads:
+            hw = net["heads"]
+            keys = ("bn_pol_mean", "bn_pol_invstd", "ip_pol_w", "ip_pol_b", "bn_val_mean",
+                    "bn_val_invstd", "ip1_val_w", "ip1_val_b", "ip2_val_w", "ip2_val_b")
+            arrs = [np.ascontiguousarray(hw[k], np.float32) for k in keys]
+            check(L.lzb_pipe_push_heads(self.h, *[_ptr(a) for a in arrs]))
+        check(L.lzb_pipe_finalize(self.h))
+
+    def context(self, max_batch):
+        return Context(self, max_batch)
+
+    def close(self):
+        if self.h:
+            lib().lzb_pipe_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Context:
+    """Stream + activation buffers on a pipe (``lzb_ctx``)."""
+
+    def __init__(self, pipe, max_batch):
+        self.pipe = pipe
+        self.max_batch = max_batch
+        self.h = ctypes.c_void_p()
+        check(lib().lzb_ctx_create(ctypes.byref(self.h), pipe.h, max_batch))
+
+    def forward(self, x):
+        """Host ``[n][18][19][19]`` fp32 -> raw head planes ``pol[n][722]``, ``val[n][361]``."""
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, IN_FLOATS)
+        n = x.shape[0]
+        pol = np.empty((n, POL_FLOATS), np.float32)
+        val = np.empty((n, VAL_FLOATS), np.float32)
+        check(lib().lzb_ctx_forward(self.h, x.ctypes.data, n, pol.ctypes.data, val.ctypes.data))
+        return pol, val
+
+    def forward_heads(self, x, softmax_temp=1.0):
+        """Host positions -> ``policy[n][362]`` (softmax) and ``winrate[n]``."""
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, IN_FLOATS)
+        n = x.shape[0]
+        policy = np.empty((n, MOVES), np.float32)
+        win = np.empty(n, np.float32)
+        check(lib().lzb_ctx_forward_heads(self.h, x.ctypes.data, n, softmax_temp,
+                                          policy.ctypes.data, win.ctypes.data))
+        return policy, win
+
+    def forward_ptr(self, in_ptr, n, pol_ptr, val_ptr):
+        """Raw host pointers (e.g. pinned buffers); blocking."""
+        check(lib().lzb_ctx_forward(self.h, in_ptr, n, pol_ptr, val_ptr))
+
+    def forward_heads_ptr(self, in_ptr, n, temp, policy_ptr, win_ptr):
+        check(lib().lzb_ctx_forward_heads(self.h, in_ptr, n, temp, policy_ptr, win_ptr))
+
+    def forward_device(self, in_dev, n, pol_dev, val_dev):
+        """Device pointers, enqueued on the context's stream; no wait."""
+        check(lib().lzb_ctx_forward_device(self.h, in_dev, n, pol_dev, val_dev))
+
+    def forward_heads_device(self, in_dev, n, temp, policy_dev, win_dev):
+        check(lib().lzb_ctx_forward_heads_device(self.h, in_dev, n, temp, policy_dev, win_dev))
+
+    def sync(self):
+        check(lib().lzb_ctx_sync(self.h))
+
+    @property
+    def stream(self):
+        return lib().lzb_ctx_stream(self.h)
+
+    def set_micro_batch(self, n):
+        check(lib().lzb_ctx_set_micro_batch(self.h, n))
+
+    @property
+    def launches(self):
+        return lib().lzb_ctx_launch_count(self.h)
+
+    def debug_conv(self, layer, x, residual=None):
+        """One 3x3 layer on fp32 NCHW host data (diagnostics)."""
+        x = np.ascontiguousarray(x, np.float32)
+        n = x.shape[0]
+        out = np.empty((n, self.pipe.channels, 361), np.float32)
+        r = None if residual is None else _ptr(np.ascontiguousarray(residual, np.float32))
+        check(lib().lzb_ctx_debug_conv(self.h, layer, _ptr(x), n, r, _ptr(out)))
+        return out
+
+    def close(self):
+        if self.h:
+            lib().lzb_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -1,0 +1,680 @@
+// C-ABI implementation of the B200 forward pipe (see include/lzb200.h).
+//
+// A pipe holds the network on one GPU: per 3x3 layer the Winograd-transformed
+// filters U[36][Kp][Cin_p] in the tower's storage type plus fp32 batch-norm
+// vectors, and the two 1x1 head filters.  A context holds a stream and the
+// activation buffers (V, M, X) sized for one micro-batch; a batch is pushed
+// through the whole tower one micro-batch at a time so that V and M, the two
+// large tensors every layer writes and reads once, stay resident in L2.
+//
+// Per 3x3 layer two kernels run: the channel contractions (tcgen05 or FFMA)
+// and the fused output-transform / batch-norm / residual / ReLU / next input
+// transform.  The sequence mirrors OpenCL_Network::forward
+// (src/OpenCL.cpp:143-329) and CPUPipe::forward (src/CPUPipe.cpp:379-428).
+#include "../../include/lzb200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "gemm_simt.cuh"
+#include "gemm_tcgen05.cuh"
+#include "head_kernels.cuh"
+#include "transform_kernels.cuh"
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(int code, const std::string& msg) {
+    g_error = msg;
+    return code;
+}
+
+#define LZB_CUDA(expr)                                                                     \
+    do {                                                                                   \
+        cudaError_t e_ = (expr);                                                           \
+        if (e_ != cudaSuccess) {                                                           \
+            return fail(LZB_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_)); \
+        }                                                                                  \
+    } while (0)
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+constexpr int kMaxMicroBatch = 256;      // rows of V/M allocated: 25 * 256 = 6400
+constexpr int kDefaultMicroBatch = 64;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up at run time so that the library loads
+// (and its symbols can be listed) on a machine without a CUDA driver.
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+    });
+    return fn;
+}
+
+// 2-D map over a row-major [rows][cols] matrix of 16-bit elements; box =
+// 64 columns (128 bytes) x box_rows, written to shared memory under the
+// 128-byte swizzle the UMMA descriptors expect.
+int make_map_2d(CUtensorMap* map, int precision, void* base, uint64_t rows, uint64_t cols,
+                uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(LZB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt =
+        precision == LZB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail(LZB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+    }
+    return LZB_OK;
+}
+
+struct Layer {
+    void* U = nullptr;          // [36][Kp][cin_p] storage type
+    float* mean = nullptr;      // [Kp]
+    float* invstd = nullptr;    // [Kp]
+    int cin_p = 0;
+    bool present = false;
+    CUtensorMap tmU;
+};
+
+struct Heads {
+    bool present = false;
+    float *bn_pol_mean = nullptr, *bn_pol_invstd = nullptr, *ip_pol_wT = nullptr,
+          *ip_pol_b = nullptr, *bn_val_mean = nullptr, *bn_val_invstd = nullptr,
+          *ip1_val_wT = nullptr, *ip1_val_b = nullptr, *ip2_val_w = nullptr, *ip2_val_b = nullptr;
+};
+
+}  // namespace
+
+struct lzb_pipe {
+    int device = 0;
+    int channels = 0;   // C
+    int Cp = 0;         // C rounded up to 64
+    int blocks = 0;
+    int precision = LZB_FP16;
+    int elt = 2;        // bytes per stored element
+    int sm_count = 0;
+    std::vector<Layer> layers;
+    float* head_w = nullptr;   // [3][Cp] fp32
+    bool head_convs = false;
+    bool finalized = false;
+    Heads heads;
+};
+
+struct lzb_ctx {
+    lzb_pipe* pipe = nullptr;
+    int max_batch = 0;
+    int micro_cap = 0;     // positions V/M/X can hold
+    int micro = 0;         // positions per pass through the tower
+    int Pa = 0;            // rows of V and M (multiple of 128)
+    cudaStream_t stream = nullptr;
+    void *V = nullptr, *M = nullptr, *X = nullptr;
+    float *d_in = nullptr, *d_pol = nullptr, *d_val = nullptr;
+    float *d_policy = nullptr, *d_winrate = nullptr;
+    int* d_err = nullptr;
+    int* h_err = nullptr;  // pinned
+    CUtensorMap tmV_first, tmV;
+    long long launches = 0;
+};
+
+namespace {
+
+using namespace lzb;
+
+template <typename T>
+int upload_layer_t(lzb_pipe* p, Layer& L, const float* U32_dev, int c_in) {
+    const size_t n = (size_t)kPoints * p->Cp * L.cin_p;
+    LZB_CUDA(cudaMalloc(&L.U, n * sizeof(T)));
+    repack_u_kernel<T><<<1024, 256>>>(U32_dev, static_cast<T*>(L.U), c_in, p->channels, L.cin_p, p->Cp);
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+int upload_padded(float** dst, const float* src, int n, int n_pad) {
+    std::vector<float> tmp(n_pad, 0.0f);
+    std::memcpy(tmp.data(), src, sizeof(float) * n);
+    LZB_CUDA(cudaMalloc(dst, sizeof(float) * n_pad));
+    LZB_CUDA(cudaMemcpy(*dst, tmp.data(), sizeof(float) * n_pad, cudaMemcpyHostToDevice));
+    return LZB_OK;
+}
+
+int upload_plain(float** dst, const float* src, size_t n) {
+    LZB_CUDA(cudaMalloc(dst, sizeof(float) * n));
+    LZB_CUDA(cudaMemcpy(*dst, src, sizeof(float) * n, cudaMemcpyHostToDevice));
+    return LZB_OK;
+}
+
+int upload_transposed(float** dst, const float* src, int rows, int cols) {
+    std::vector<float> t((size_t)rows * cols);
+    for (int r = 0; r < rows; r++)
+        for (int c = 0; c < cols; c++) t[(size_t)c * rows + r] = src[(size_t)r * cols + c];
+    return upload_plain(dst, t.data(), t.size());
+}
+
+// ---- launches -------------------------------------------------------------
+
+template <typename T>
+int launch_gemm(lzb_ctx* c, const Layer& L, int P) {
+    lzb_pipe* p = c->pipe;
+    if (p->precision == LZB_FP32) {
+        const dim3 grid(round_up(P, kSimtTile) / kSimtTile, p->Cp / kSimtTile, kPoints);
+        gemm_f32_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const float*>(c->V),
+                                                     static_cast<const float*>(L.U),
+                                                     static_cast<float*>(c->M), c->Pa, L.cin_p, p->Cp);
+    }
+    c->launches++;
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+template <typename T>
+int launch_gemm_tc(lzb_ctx* c, const Layer& L, int P, bool first) {
+    lzb_pipe* p = c->pipe;
+    const int nblk = (P + tc::kBlockM - 1) / tc::kBlockM;
+    const int items = kPoints * nblk;
+    const int grid = items < p->sm_count ? items : p->sm_count;
+    tc::gemm_tc_kernel<T><<<grid, tc::kThreads, tc::kSmemBytes, c->stream>>>(
+        first ? c->tmV_first : c->tmV, L.tmU, static_cast<T*>(c->M), c->Pa, P, p->Cp,
+        L.cin_p / tc::kChunkK, nblk, c->d_err);
+    c->launches++;
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+template <typename T>
+int contraction(lzb_ctx* c, const Layer& L, int P, bool first) {
+    if (c->pipe->precision == LZB_FP32) return launch_gemm<float>(c, L, P);
+    return launch_gemm_tc<T>(c, L, P, first);
+}
+template <>
+int contraction<float>(lzb_ctx* c, const Layer& L, int P, bool) {
+    return launch_gemm<float>(c, L, P);
+}
+
+template <typename T>
+int launch_xform(lzb_ctx* c, const Layer& L, int nb, const T* R, T* X_out, T* V) {
+    lzb_pipe* p = c->pipe;
+    const dim3 grid(p->Cp / kChanPerCta, nb);
+    const size_t smem = (size_t)kBoardCells * 32 * 2 * sizeof(T);
+    xform_kernel<T><<<grid, kXformThreads, smem, c->stream>>>(
+        static_cast<const T*>(c->M), c->Pa, p->Cp, L.mean, L.invstd, R, X_out, V);
+    c->launches++;
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+// One micro-batch (nb positions, device pointers) through the whole tower.
+template <typename T>
+int run_tower(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* val_dev) {
+    lzb_pipe* p = c->pipe;
+    const int P = nb * kTilesPerPos;
+    T* V = static_cast<T*>(c->V);
+    T* X = static_cast<T*>(c->X);
+    int rc;
+    first_in_transform_kernel<T><<<(P + 7) / 8, 256, 0, c->stream>>>(in_dev, V, c->Pa, P);
+    c->launches++;
+    LZB_CUDA(cudaGetLastError());
+    if ((rc = contraction<T>(c, p->layers[0], P, true))) return rc;
+    if ((rc = launch_xform<T>(c, p->layers[0], nb, nullptr, X, p->blocks ? V : nullptr))) return rc;
+    for (int b = 0; b < p->blocks; b++) {
+        const Layer& l1 = p->layers[1 + 2 * b];
+        const Layer& l2 = p->layers[2 + 2 * b];
+        if ((rc = contraction<T>(c, l1, P, false))) return rc;
+        if ((rc = launch_xform<T>(c, l1, nb, nullptr, nullptr, V))) return rc;
+        if ((rc = contraction<T>(c, l2, P, false))) return rc;
+        const bool last = (b + 1 == p->blocks);
+        if ((rc = launch_xform<T>(c, l2, nb, X, X, last ? nullptr : V))) return rc;
+    }
+    const int cells = nb * kSq;
+    head_conv_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(X, p->head_w, p->Cp, cells, pol_dev,
+                                                                 val_dev);
+    c->launches++;
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+int run_tower_any(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* val_dev) {
+    switch (c->pipe->precision) {
+        case LZB_FP32: return run_tower<float>(c, in_dev, nb, pol_dev, val_dev);
+        case LZB_FP16: return run_tower<__half>(c, in_dev, nb, pol_dev, val_dev);
+        default: return run_tower<__nv_bfloat16>(c, in_dev, nb, pol_dev, val_dev);
+    }
+}
+
+int check_ctx(lzb_ctx* c, int n) {
+    if (!c || !c->pipe) return fail(LZB_ERR_ARG, "null context");
+    if (!c->pipe->finalized) return fail(LZB_ERR_ARG, "pipe not finalized");
+    if (n < 1 || n > c->max_batch) {
+        return fail(LZB_ERR_ARG, "batch " + std::to_string(n) + " outside 1.." +
+                                     std::to_string(c->max_batch));
+    }
+    return LZB_OK;
+}
+
+int set_smem_attrs() {
+    LZB_CUDA(cudaFuncSetAttribute(xform_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kBoardCells * 32 * 2 * 4));
+    LZB_CUDA(cudaFuncSetAttribute(in_transform_kernel<float>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kBoardCells * 32 * 2 * 4));
+    LZB_CUDA(cudaFuncSetAttribute(xform_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kBoardCells * 32 * 2 * 2));
+    LZB_CUDA(cudaFuncSetAttribute(xform_kernel<__nv_bfloat16>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kBoardCells * 32 * 2 * 2));
+    LZB_CUDA(cudaFuncSetAttribute(in_transform_kernel<__half>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kBoardCells * 32 * 2 * 2));
+    LZB_CUDA(cudaFuncSetAttribute(in_transform_kernel<__nv_bfloat16>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kBoardCells * 32 * 2 * 2));
+    LZB_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<__half>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<__nv_bfloat16>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes));
+    return LZB_OK;
+}
+
+}  // namespace
+
+namespace {
+using namespace lzb;
+template <typename T>
+int debug_conv_t(lzb_ctx* c, int layer, const float* in, int n, const float* residual, float* out) {
+    lzb_pipe* p = c->pipe;
+    const Layer& L = p->layers[layer];
+    const int P = n * kTilesPerPos;
+    const int C = p->channels;
+    const size_t plane_floats = (size_t)n * C * kSq;
+    T* V = static_cast<T*>(c->V);
+    T* X = static_cast<T*>(c->X);
+    float* stage = nullptr;    // fp32 NCHW staging on the device
+    LZB_CUDA(cudaMalloc(&stage, sizeof(float) * (plane_floats > (size_t)n * LZB_IN_FLOATS
+                                                     ? plane_floats
+                                                     : (size_t)n * LZB_IN_FLOATS)));
+    int rc = LZB_OK;
+    auto guard = [&](cudaError_t e, const char* what) {
+        if (rc == LZB_OK && e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+    };
+    if (layer == 0) {
+        guard(cudaMemcpyAsync(stage, in, sizeof(float) * n * LZB_IN_FLOATS, cudaMemcpyHostToDevice, c->stream), "copy in");
+        first_in_transform_kernel<T><<<(P + 7) / 8, 256, 0, c->stream>>>(stage, V, c->Pa, P);
+    } else {
+        guard(cudaMemcpyAsync(stage, in, sizeof(float) * plane_floats, cudaMemcpyHostToDevice, c->stream), "copy in");
+        nchw_to_nhwc_kernel<T><<<512, 256, 0, c->stream>>>(stage, X, n, C, p->Cp);
+        const dim3 grid(p->Cp / kChanPerCta, n);
+        in_transform_kernel<T><<<grid, kXformThreads, (size_t)kBoardCells * 32 * 2 * sizeof(T), c->stream>>>(
+            X, V, c->Pa, p->Cp);
+    }
+    guard(cudaGetLastError(), "input transform");
+    if (rc == LZB_OK) rc = contraction<T>(c, L, P, layer == 0);
+    const T* R = nullptr;
+    if (rc == LZB_OK && residual) {
+        guard(cudaMemcpyAsync(stage, residual, sizeof(float) * plane_floats, cudaMemcpyHostToDevice, c->stream), "copy residual");
+        nchw_to_nhwc_kernel<T><<<512, 256, 0, c->stream>>>(stage, X, n, C, p->Cp);
+        R = X;
+    }
+    if (rc == LZB_OK) rc = launch_xform<T>(c, L, n, R, X, nullptr);
+    if (rc == LZB_OK) {
+        nhwc_to_nchw_kernel<T><<<512, 256, 0, c->stream>>>(X, stage, n, C, p->Cp);
+        guard(cudaGetLastError(), "layout conversion");
+        guard(cudaMemcpyAsync(out, stage, sizeof(float) * plane_floats, cudaMemcpyDeviceToHost, c->stream), "copy out");
+    }
+    int rc2 = lzb_ctx_sync(c);
+    cudaFree(stage);
+    return rc ? rc : rc2;
+}
+}  // namespace
+
+// ===========================================================================
+// C ABI
+// ===========================================================================
+
+extern "C" {
+
+const char* lzb_last_error(void) { return g_error.c_str(); }
+
+int lzb_device_count(int* count) {
+    if (!count) return fail(LZB_ERR_ARG, "null count");
+    *count = 0;
+    LZB_CUDA(cudaGetDeviceCount(count));
+    return LZB_OK;
+}
+
+int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int precision) {
+    if (!out) return fail(LZB_ERR_ARG, "null out");
+    *out = nullptr;
+    if (channels < 1 || blocks < 0) return fail(LZB_ERR_ARG, "bad channels/blocks");
+    if (precision != LZB_FP32 && precision != LZB_FP16 && precision != LZB_BF16) {
+        return fail(LZB_ERR_ARG, "unknown precision");
+    }
+    const int Cp = round_up(channels, 64);
+    if (precision != LZB_FP32 && Cp > tc::kMaxN) {
+        return fail(LZB_ERR_ARG, "tensor-core path supports at most 256 filters; use LZB_FP32");
+    }
+    LZB_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    LZB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        return fail(LZB_ERR_CUDA, std::string("device ") + prop.name +
+                                      " is not compute capability 10.x; this library is sm_100a only");
+    }
+    int rc = set_smem_attrs();
+    if (rc) return rc;
+    lzb_pipe* p = new lzb_pipe;
+    p->device = device;
+    p->channels = channels;
+    p->Cp = Cp;
+    p->blocks = blocks;
+    p->precision = precision;
+    p->elt = precision == LZB_FP32 ? 4 : 2;
+    p->sm_count = prop.multiProcessorCount;
+    p->layers.resize(1 + 2 * blocks);
+    *out = p;
+    return LZB_OK;
+}
+
+void lzb_pipe_destroy(lzb_pipe* p) {
+    if (!p) return;
+    cudaSetDevice(p->device);
+    for (auto& L : p->layers) {
+        cudaFree(L.U);
+        cudaFree(L.mean);
+        cudaFree(L.invstd);
+    }
+    cudaFree(p->head_w);
+    Heads& h = p->heads;
+    float* hs[] = {h.bn_pol_mean, h.bn_pol_invstd, h.ip_pol_wT, h.ip_pol_b, h.bn_val_mean,
+                   h.bn_val_invstd, h.ip1_val_wT, h.ip1_val_b, h.ip2_val_w, h.ip2_val_b};
+    for (float* q : hs) cudaFree(q);
+    delete p;
+}
+
+int lzb_pipe_push_conv(lzb_pipe* p, int layer, const float* U, int c_in, const float* bn_mean,
+                       const float* bn_invstd) {
+    if (!p || !U || !bn_mean || !bn_invstd) return fail(LZB_ERR_ARG, "null argument");
+    if (p->finalized) return fail(LZB_ERR_ARG, "pipe already finalized");
+    if (layer < 0 || layer >= (int)p->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
+    const int want = layer == 0 ? kInputPlanes : p->channels;
+    if (c_in != want) return fail(LZB_ERR_ARG, "c_in does not match the layer");
+    LZB_CUDA(cudaSetDevice(p->device));
+    Layer& L = p->layers[layer];
+    if (L.present) return fail(LZB_ERR_ARG, "layer pushed twice");
+    L.cin_p = round_up(c_in, 64);
+    float* U32 = nullptr;
+    const size_t n32 = (size_t)kPoints * c_in * p->channels;
+    LZB_CUDA(cudaMalloc(&U32, n32 * sizeof(float)));
+    cudaError_t e = cudaMemcpy(U32, U, n32 * sizeof(float), cudaMemcpyHostToDevice);
+    int rc = LZB_OK;
+    if (e != cudaSuccess) {
+        rc = fail(LZB_ERR_CUDA, std::string("weight upload: ") + cudaGetErrorString(e));
+    } else if (p->precision == LZB_FP32) {
+        rc = upload_layer_t<float>(p, L, U32, c_in);
+    } else if (p->precision == LZB_FP16) {
+        rc = upload_layer_t<__half>(p, L, U32, c_in);
+    } else {
+        rc = upload_layer_t<__nv_bfloat16>(p, L, U32, c_in);
+    }
+    if (rc == LZB_OK) {
+        e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("weight repack: ") + cudaGetErrorString(e));
+    }
+    cudaFree(U32);
+    if (rc) return rc;
+    if ((rc = upload_padded(&L.mean, bn_mean, p->channels, p->Cp))) return rc;
+    if ((rc = upload_padded(&L.invstd, bn_invstd, p->channels, p->Cp))) return rc;
+    if (p->precision != LZB_FP32) {
+        rc = make_map_2d(&L.tmU, p->precision, L.U, (uint64_t)kPoints * p->Cp, L.cin_p, p->Cp);
+        if (rc) return rc;
+    }
+    L.present = true;
+    return LZB_OK;
+}
+
+int lzb_pipe_push_head_convs(lzb_pipe* p, const float* pol_w, const float* val_w) {
+    if (!p || !pol_w || !val_w) return fail(LZB_ERR_ARG, "null argument");
+    if (p->finalized) return fail(LZB_ERR_ARG, "pipe already finalized");
+    LZB_CUDA(cudaSetDevice(p->device));
+    std::vector<float> w((size_t)3 * p->Cp, 0.0f);
+    for (int c = 0; c < p->channels; c++) {
+        w[c] = pol_w[c];
+        w[p->Cp + c] = pol_w[p->channels + c];
+        w[2 * p->Cp + c] = val_w[c];
+    }
+    if (p->head_w) cudaFree(p->head_w);
+    int rc = upload_plain(&p->head_w, w.data(), w.size());
+    if (rc) return rc;
+    p->head_convs = true;
+    return LZB_OK;
+}
+
+int lzb_pipe_push_heads(lzb_pipe* p, const float* bn_pol_mean, const float* bn_pol_invstd,
+                        const float* ip_pol_w, const float* ip_pol_b, const float* bn_val_mean,
+                        const float* bn_val_invstd, const float* ip1_val_w, const float* ip1_val_b,
+                        const float* ip2_val_w, const float* ip2_val_b) {
+    if (!p || !bn_pol_mean || !bn_pol_invstd || !ip_pol_w || !ip_pol_b || !bn_val_mean ||
+        !bn_val_invstd || !ip1_val_w || !ip1_val_b || !ip2_val_w || !ip2_val_b) {
+        return fail(LZB_ERR_ARG, "null argument");
+    }
+    if (p->heads.present) return fail(LZB_ERR_ARG, "heads pushed twice");
+    LZB_CUDA(cudaSetDevice(p->device));
+    Heads& h = p->heads;
+    int rc;
+    if ((rc = upload_plain(&h.bn_pol_mean, bn_pol_mean, 2))) return rc;
+    if ((rc = upload_plain(&h.bn_pol_invstd, bn_pol_invstd, 2))) return rc;
+    if ((rc = upload_transposed(&h.ip_pol_wT, ip_pol_w, kMoves, 2 * kSq))) return rc;
+    if ((rc = upload_plain(&h.ip_pol_b, ip_pol_b, kMoves))) return rc;
+    if ((rc = upload_plain(&h.bn_val_mean, bn_val_mean, 1))) return rc;
+    if ((rc = upload_plain(&h.bn_val_invstd, bn_val_invstd, 1))) return rc;
+    if ((rc = upload_transposed(&h.ip1_val_wT, ip1_val_w, kValueHidden, kSq))) return rc;
+    if ((rc = upload_plain(&h.ip1_val_b, ip1_val_b, kValueHidden))) return rc;
+    if ((rc = upload_plain(&h.ip2_val_w, ip2_val_w, kValueHidden))) return rc;
+    if ((rc = upload_plain(&h.ip2_val_b, ip2_val_b, 1))) return rc;
+    h.present = true;
+    return LZB_OK;
+}
+
+int lzb_pipe_finalize(lzb_pipe* p) {
+    if (!p) return fail(LZB_ERR_ARG, "null pipe");
+    for (size_t l = 0; l < p->layers.size(); l++) {
+        if (!p->layers[l].present) return fail(LZB_ERR_ARG, "layer " + std::to_string(l) + " missing");
+    }
+    if (!p->head_convs) return fail(LZB_ERR_ARG, "head convolutions missing");
+    p->finalized = true;
+    return LZB_OK;
+}
+
+int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
+    if (!out) return fail(LZB_ERR_ARG, "null out");
+    *out = nullptr;
+    if (!p || !p->finalized) return fail(LZB_ERR_ARG, "pipe not finalized");
+    if (max_batch < 1 || max_batch > (1 << 16)) return fail(LZB_ERR_ARG, "bad max_batch");
+    LZB_CUDA(cudaSetDevice(p->device));
+    lzb_ctx* c = new lzb_ctx;
+    c->pipe = p;
+    c->max_batch = max_batch;
+    c->micro_cap = max_batch < kMaxMicroBatch ? max_batch : kMaxMicroBatch;
+    c->micro = c->micro_cap < kDefaultMicroBatch ? c->micro_cap : kDefaultMicroBatch;
+    c->Pa = round_up(c->micro_cap * kTilesPerPos, 128);
+    const size_t vm = (size_t)kPoints * c->Pa * p->Cp * p->elt;
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](void** ptr, size_t bytes) {
+        if (e == cudaSuccess) e = cudaMalloc(ptr, bytes);
+        if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
+    };
+    alloc(&c->V, vm);
+    alloc(&c->M, vm);
+    alloc(&c->X, (size_t)c->micro_cap * kSq * p->Cp * p->elt);
+    alloc((void**)&c->d_in, (size_t)max_batch * LZB_IN_FLOATS * sizeof(float));
+    alloc((void**)&c->d_pol, (size_t)max_batch * LZB_POL_FLOATS * sizeof(float));
+    alloc((void**)&c->d_val, (size_t)max_batch * LZB_VAL_FLOATS * sizeof(float));
+    alloc((void**)&c->d_policy, (size_t)max_batch * LZB_MOVES * sizeof(float));
+    alloc((void**)&c->d_winrate, (size_t)max_batch * sizeof(float));
+    alloc((void**)&c->d_err, sizeof(int));
+    if (e == cudaSuccess) e = cudaMallocHost((void**)&c->h_err, sizeof(int));
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+        const int code = (e == cudaErrorMemoryAllocation) ? LZB_ERR_NOMEM : LZB_ERR_CUDA;
+        fail(code, std::string("context allocation: ") + cudaGetErrorString(e));
+        lzb_ctx_destroy(c);
+        return code;
+    }
+    *c->h_err = 0;
+    if (p->precision != LZB_FP32) {
+        int rc = make_map_2d(&c->tmV_first, p->precision, c->V, (uint64_t)kPoints * c->Pa, 64, tc::kBlockM);
+        if (!rc) rc = make_map_2d(&c->tmV, p->precision, c->V, (uint64_t)kPoints * c->Pa, p->Cp, tc::kBlockM);
+        if (rc) {
+            lzb_ctx_destroy(c);
+            return rc;
+        }
+    }
+    *out = c;
+    return LZB_OK;
+}
+
+void lzb_ctx_destroy(lzb_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->pipe->device);
+    if (c->stream) {
+        cudaStreamSynchronize(c->stream);
+        cudaStreamDestroy(c->stream);
+    }
+    void* ptrs[] = {c->V, c->M, c->X, c->d_in, c->d_pol, c->d_val, c->d_policy, c->d_winrate, c->d_err};
+    for (void* q : ptrs) cudaFree(q);
+    if (c->h_err) cudaFreeHost(c->h_err);
+    delete c;
+}
+
+int lzb_ctx_set_micro_batch(lzb_ctx* c, int positions) {
+    if (!c) return fail(LZB_ERR_ARG, "null context");
+    if (positions == 0) positions = kDefaultMicroBatch;
+    if (positions < 1) return fail(LZB_ERR_ARG, "bad micro-batch");
+    c->micro = positions < c->micro_cap ? positions : c->micro_cap;
+    return LZB_OK;
+}
+
+long long lzb_ctx_launch_count(const lzb_ctx* c) { return c ? c->launches : 0; }
+
+void* lzb_ctx_stream(lzb_ctx* c) { return c ? (void*)c->stream : nullptr; }
+
+int lzb_ctx_forward_device(lzb_ctx* c, const float* in_dev, int n, float* pol_dev, float* val_dev) {
+    int rc = check_ctx(c, n);
+    if (rc) return rc;
+    if (!in_dev || !pol_dev || !val_dev) return fail(LZB_ERR_ARG, "null buffer");
+    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    for (int off = 0; off < n; off += c->micro) {
+        const int nb = (n - off) < c->micro ? (n - off) : c->micro;
+        rc = run_tower_any(c, in_dev + (size_t)off * LZB_IN_FLOATS, nb,
+                           pol_dev + (size_t)off * LZB_POL_FLOATS,
+                           val_dev + (size_t)off * LZB_VAL_FLOATS);
+        if (rc) return rc;
+    }
+    return LZB_OK;
+}
+
+int lzb_ctx_sync(lzb_ctx* c) {
+    if (!c) return fail(LZB_ERR_ARG, "null context");
+    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+    LZB_CUDA(cudaStreamSynchronize(c->stream));
+    if (*c->h_err != 0) {
+        const int code = *c->h_err;
+        *c->h_err = 0;
+        cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
+        return fail(LZB_ERR_DEVICE_WAIT,
+                    "a kernel gave up a bounded wait (code " + std::to_string(code) + ")");
+    }
+    return LZB_OK;
+}
+
+int lzb_ctx_forward(lzb_ctx* c, const float* in, int n, float* pol, float* val) {
+    int rc = check_ctx(c, n);
+    if (rc) return rc;
+    if (!in || !pol || !val) return fail(LZB_ERR_ARG, "null buffer");
+    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(cudaMemcpyAsync(c->d_in, in, (size_t)n * LZB_IN_FLOATS * sizeof(float),
+                             cudaMemcpyHostToDevice, c->stream));
+    if ((rc = lzb_ctx_forward_device(c, c->d_in, n, c->d_pol, c->d_val))) return rc;
+    LZB_CUDA(cudaMemcpyAsync(pol, c->d_pol, (size_t)n * LZB_POL_FLOATS * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+    LZB_CUDA(cudaMemcpyAsync(val, c->d_val, (size_t)n * LZB_VAL_FLOATS * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+    return lzb_ctx_sync(c);
+}
+
+int lzb_ctx_forward_heads_device(lzb_ctx* c, const float* in_dev, int n, float softmax_temp,
+                                 float* policy_dev, float* winrate_dev) {
+    int rc = check_ctx(c, n);
+    if (rc) return rc;
+    if (!c->pipe->heads.present) return fail(LZB_ERR_ARG, "head weights were not pushed");
+    if (!(softmax_temp > 0.f)) return fail(LZB_ERR_ARG, "softmax temperature must be positive");
+    if (!policy_dev || !winrate_dev) return fail(LZB_ERR_ARG, "null buffer");
+    if ((rc = lzb_ctx_forward_device(c, in_dev, n, c->d_pol, c->d_val))) return rc;
+    const Heads& h = c->pipe->heads;
+    policy_head_kernel<<<n, 384, 0, c->stream>>>(c->d_pol, h.bn_pol_mean, h.bn_pol_invstd, h.ip_pol_wT,
+                                                 h.ip_pol_b, 1.0f / softmax_temp, policy_dev);
+    value_head_kernel<<<n, 256, 0, c->stream>>>(c->d_val, h.bn_val_mean, h.bn_val_invstd, h.ip1_val_wT,
+                                                h.ip1_val_b, h.ip2_val_w, h.ip2_val_b, winrate_dev);
+    c->launches += 2;
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+int lzb_ctx_forward_heads(lzb_ctx* c, const float* in, int n, float softmax_temp, float* policy,
+                          float* winrate) {
+    int rc = check_ctx(c, n);
+    if (rc) return rc;
+    if (!in || !policy || !winrate) return fail(LZB_ERR_ARG, "null buffer");
+    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(cudaMemcpyAsync(c->d_in, in, (size_t)n * LZB_IN_FLOATS * sizeof(float),
+                             cudaMemcpyHostToDevice, c->stream));
+    if ((rc = lzb_ctx_forward_heads_device(c, c->d_in, n, softmax_temp, c->d_policy, c->d_winrate))) {
+        return rc;
+    }
+    LZB_CUDA(cudaMemcpyAsync(policy, c->d_policy, (size_t)n * LZB_MOVES * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+    LZB_CUDA(cudaMemcpyAsync(winrate, c->d_winrate, (size_t)n * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+    return lzb_ctx_sync(c);
+}
+
+int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n, const float* residual,
+                       float* out) {
+    if (!c || !c->pipe || !c->pipe->finalized) return fail(LZB_ERR_ARG, "context not ready");
+    if (n < 1 || n > c->micro_cap) return fail(LZB_ERR_ARG, "batch outside the micro-batch capacity");
+    if (layer < 0 || layer >= (int)c->pipe->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
+    if (!in || !out) return fail(LZB_ERR_ARG, "null buffer");
+    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    switch (c->pipe->precision) {
+        case LZB_FP32: return debug_conv_t<float>(c, layer, in, n, residual, out);
+        case LZB_FP16: return debug_conv_t<__half>(c, layer, in, n, residual, out);
+        default: return debug_conv_t<__nv_bfloat16>(c, layer, in, n, residual, out);
+    }
+}
+
+}  // extern "C"
