@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Throughput of the forward pipe on the headline workload.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (config 3): 40 residual blocks x 256 filters, fp16 operands with fp32
+accumulation, 256 positions per GPU per step, random-init weights and
+synthetic positions.  A step is one complete evaluation of a batch: tower, 1x1
+head convolutions and the policy/value heads.
+
+Prints ONE JSON line.  `value` is positions/second with the inputs already in
+HBM; `e2e` is the same metric through the host-buffer entry point of the C ABI
+(pinned host memory, copies inside the timed region).  With N > 1 the script is
+launched by torch.distributed.run, one rank per GPU; positions are sharded, the
+path has no collective, so the process group only serves the barrier and the
+max-over-ranks of the device times.
+
+`--impl reference` times the reference's own CPU implementation (CPUPipe
+compiled unchanged, OpenBLAS, one thread per core) on a bounded sample of the
+same workload.
+"""
+import argparse
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+BLOCKS, FILTERS, BATCH = 40, 256, 256
+WEIGHT_SEED, INPUT_SEED = 2003, 1003
+PRECISION = "fp16"
+# direct-convolution FLOPs per position, tower + 1x1 convs + the three FC layers
+FLOPS_DIRECT = (2 * 9 * 18 * FILTERS * 361 + 2 * BLOCKS * 2 * 9 * FILTERS * FILTERS * 361
+                + 2 * FILTERS * 3 * 361 + 708072)
+# executed by one launch of the contraction kernel per position: 36 points x 25 tiles x C x K MACs
+FLOPS_GEMM_PER_POS = 2 * 36 * 25 * FILTERS * FILTERS
+# DRAM traffic of one contraction launch (64 positions), from the committed ncu capture; None until measured
+GEMM_DRAM_BYTES_PER_LAUNCH = None
+
+
+def load_package():
+    path = os.path.join(ROOT, "leela-zero_b200", "__init__.py")
+    spec = importlib.util.spec_from_file_location(
+        "leela_zero_b200", path, submodule_search_locations=[os.path.dirname(path)])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["leela_zero_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "hbm_gbs": d["hbm_gbs"], "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(device), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.tmp.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, parts[2:]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        self.tmp.close()
+        os.unlink(self.tmp.name)
+        if sm:
+            sm.sort()
+            out = {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+def cpu_reference_rate(net, weights_mod, positions, threads):
+    """positions/s of the reference CPUPipe (or the C port) on host cores."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as O
+    kind = "reference" if O.ref_available() else "port"
+    if kind == "port":
+        threads = 1
+    pipe = O.cpu_pipe(net)
+    x = weights_mod.synthetic_positions(positions, INPUT_SEED + 7)
+    pipe.forward(x[:1])  # page the weights in
+    t0 = time.perf_counter()
+    if kind == "reference":
+        pipe.forward(x, threads=threads)
+    else:
+        pipe.forward(x)
+    dt = time.perf_counter() - t0
+    return positions / dt, kind, threads, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    pkg_w = load_package().weights
+    cores = os.cpu_count() or 1
+    net = pkg_w.synthetic_network(BLOCKS, FILTERS, WEIGHT_SEED)
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import oracle as O
+    kind = "reference" if O.ref_available() else "port"
+    threads = cores if kind == "reference" else 1
+    pipe = O.cpu_pipe(net)
+    per_step = threads  # one position per thread per step
+    x = pkg_w.synthetic_positions(per_step, INPUT_SEED + 7)
+    def run():
+        pol, val = pipe.forward(x, threads=threads) if kind == "reference" else pipe.forward(x)
+        return O.heads(net, pol, val)
+    for _ in range(args.warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        run()
+    dt = time.perf_counter() - t0
+    value = per_step * args.steps / dt
+    sample = "%d positions per step (one per thread), %d steps" % (per_step, args.steps)
+    print(json.dumps({
+        "impl": "reference", "metric": "positions/sec", "value": value, "unit": "positions/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "40b x 256f tower + heads, CPUPipe on host cores",
+                   "blocks": BLOCKS, "filters": FILTERS},
+        "cpu_baseline": {"value": value, "unit": "positions/s", "cores": threads, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "positions/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="cuda", choices=["cuda", "reference"])
+    ap.add_argument("--micro-batch", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import numpy as np
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+
+    pkg = load_package()
+    W = pkg.weights
+    net = W.synthetic_network(BLOCKS, FILTERS, WEIGHT_SEED)
+    pipe = pkg.Pipe(net, PRECISION, device=local)
+    B = args.batch
+    ctx = pipe.context(B)
+    if args.micro_batch:
+        ctx.set_micro_batch(args.micro_batch)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+
+    # rotating input batches: host (pinned) and device copies
+    ROT = 4
+    x_np = W.synthetic_positions(ROT * B, INPUT_SEED + rank).reshape(ROT, B, -1)
+    x_host = torch.from_numpy(x_np).pin_memory()
+    x_dev = x_host.to(dev)
+    policy_dev = torch.empty(B, 362, device=dev)
+    win_dev = torch.empty(B, device=dev)
+    policy_host = torch.empty(B, 362).pin_memory()
+    win_host = torch.empty(B).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # 2 x L2
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def step_device(i):
+        ctx.forward_heads_device(x_dev[i % ROT].data_ptr(), B, 1.0, policy_dev.data_ptr(),
+                                 win_dev.data_ptr())
+
+    def step_host(i):
+        ctx.forward_heads_ptr(x_host[i % ROT].data_ptr(), B, 1.0, policy_host.data_ptr(),
+                              win_host.data_ptr())
+
+    def timed(step_fn, steps, warmup):
+        for i in range(warmup):
+            step_fn(i)
+        ctx.sync()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(steps)]
+        barrier()
+        torch.cuda.synchronize()
+        launches0 = ctx.launches
+        with torch.cuda.stream(stream):
+            for i in range(steps):
+                flush.zero_()                      # evict L2 between timed iterations
+                ev[i][0].record(stream)
+                step_fn(warmup + i)
+                ev[i][1].record(stream)
+        ctx.sync()
+        torch.cuda.synchronize()
+        barrier()
+        ms = sum(a.elapsed_time(b) for a, b in ev)
+        launches = ctx.launches - launches0
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps, launches
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms_dev, launches = timed(step_device, args.steps, args.warmup)
+    ms_e2e, _ = timed(step_host, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+
+    # per-kernel durations of the same workload, measured with CUDA events on
+    # the launching stream in extra steps right after the timed ones
+    ctx.profile_begin()
+    prof_steps = 3
+    for i in range(prof_steps):
+        step_device(i)
+    prof = ctx.profile_end()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        value = world * B / (ms_dev * 1e-3)
+        e2e = world * B / (ms_e2e * 1e-3)
+        g_ms, g_n = prof["contraction"]
+        micro = args.micro_batch or min(64, B)
+        # every contraction launch but the input layer's covers one micro-batch of tower work
+        flops_per_launch = FLOPS_GEMM_PER_POS * micro
+        avg_s = (g_ms / max(g_n, 1)) * 1e-3
+        achieved = flops_per_launch / avg_s / 1e12 if avg_s > 0 else 0.0
+        peak = peaks["bf16_tflops_sustained"]
+        total_ms = sum(v[0] for v in prof.values())
+        out = {
+            "metric": "positions/sec", "value": value, "unit": "positions/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "config 3: 40 blocks x 256 filters, %d positions per GPU per step, "
+                                   "tower + 1x1 head convs + policy/value heads on device" % B,
+                       "blocks": BLOCKS, "filters": FILTERS, "batch_per_gpu": B,
+                       "micro_batch": micro, "parallelism": "replicas, positions sharded, no collective",
+                       "l2": "256 MB buffer written between timed steps (L2 flush); weights 378 MB > L2"},
+            "e2e": {"value": e2e, "unit": "positions/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": B * 18 * 361 * 4, "d2h_bytes_per_step": B * 363 * 4},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "tensor_credit": {
+                "note": "direct-convolution FLOPs per position x positions/s over measured bf16 peak",
+                "flops_per_position": FLOPS_DIRECT,
+                "tflops": value * FLOPS_DIRECT / 1e12,
+                "frac_of_burst_peak": value * FLOPS_DIRECT / 1e12 / peaks["bf16_tflops"],
+                "frac_of_sustained_peak": value * FLOPS_DIRECT / 1e12 / peaks["bf16_tflops_sustained"],
+                "per_gpu_tflops": value * FLOPS_DIRECT / 1e12 / world},
+            "roofline": {"kernel": "gemm_tc_kernel (36 channel contractions, tcgen05)",
+                         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
+                         "flops_per_launch": flops_per_launch, "avg_launch_ms": avg_s * 1e3,
+                         "traffic": GEMM_DRAM_BYTES_PER_LAUNCH},
+            "kernel_time_share": {k: (v[0] / total_ms if total_ms else 0.0) for k, v in prof.items()},
+            "kernel_ms_per_step": {k: v[0] / prof_steps for k, v in prof.items()},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            cores = os.cpu_count() or 1
+            sys.path.insert(0, os.path.join(ROOT, "oracle"))
+            import oracle as O
+            npos = 2 * cores if O.ref_available() else 2
+            rate, kind, threads, dt = cpu_reference_rate(net, W, npos, cores)
+            out["cpu_baseline"] = {"value": rate, "unit": "positions/s", "cores": threads, "kind": kind,
+                                   "sample": "%d positions of the same network, %d threads, %.1f s"
+                                             % (npos, threads, dt)}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -154,6 +154,18 @@ int lzb_ctx_set_micro_batch(lzb_ctx* c, int positions);
 long long lzb_ctx_launch_count(const lzb_ctx* c);
 
 /*
+ * Per-kernel timing (diagnostics; adds two CUDA events per launch while on).
+ * Between begin and end every launch of this context is timed on its stream;
+ * end waits for the stream and returns, per kernel class, the summed
+ * durations in milliseconds and the launch counts.  Classes: 0 channel
+ * contractions, 1 fused transforms, 2 input-plane transform, 3 head kernels.
+ * The reference has this only inside its tuner (OpenCL event profiling,
+ * src/Tuner.cpp:452-453, 542-546).
+ */
+int lzb_ctx_profile_begin(lzb_ctx* c);
+int lzb_ctx_profile_end(lzb_ctx* c, double ms_by_class[4], long long launches_by_class[4]);
+
+/*
  * Diagnostics for tests: run one 3x3 layer (input transform, contraction,
  * output transform + batch-norm [+ residual] + ReLU) on n positions given as
  * fp32 NCHW host arrays and return the fp32 NCHW result.  layer 0 takes

@@ -10,6 +10,8 @@ import os
 
 import numpy as np
 
+from . import weights  # noqa: F401  (loader, preparation, synthetic data)
+
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "liblzb200.so")
 
@@ -24,7 +26,7 @@ SYMBOLS = (
     "lzb_pipe_finalize", "lzb_ctx_create", "lzb_ctx_destroy", "lzb_ctx_forward",
     "lzb_ctx_forward_device", "lzb_ctx_forward_heads", "lzb_ctx_forward_heads_device",
     "lzb_ctx_sync", "lzb_ctx_stream", "lzb_ctx_set_micro_batch", "lzb_ctx_launch_count",
-    "lzb_ctx_debug_conv",
+    "lzb_ctx_debug_conv", "lzb_ctx_profile_begin", "lzb_ctx_profile_end",
 )
 
 _f32p = ctypes.POINTER(ctypes.c_float)
@@ -65,6 +67,8 @@ def lib():
         L.lzb_ctx_set_micro_batch.argtypes = [vp, ctypes.c_int]
         L.lzb_ctx_launch_count.argtypes = [vp]
         L.lzb_ctx_debug_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
+        L.lzb_ctx_profile_begin.argtypes = [vp]
+        L.lzb_ctx_profile_end.argtypes = [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]
         _lib = L
     return _lib
 
@@ -187,6 +191,17 @@ class Context:
     @property
     def launches(self):
         return lib().lzb_ctx_launch_count(self.h)
+
+    def profile_begin(self):
+        check(lib().lzb_ctx_profile_begin(self.h))
+
+    def profile_end(self):
+        """-> {class name: (milliseconds, launches)} since profile_begin."""
+        ms = (ctypes.c_double * 4)()
+        cnt = (ctypes.c_longlong * 4)()
+        check(lib().lzb_ctx_profile_end(self.h, ms, cnt))
+        names = ("contraction", "transform", "input", "head")
+        return {k: (ms[i], cnt[i]) for i, k in enumerate(names)}
 
     def debug_conv(self, layer, x, residual=None):
         """One 3x3 layer on fp32 NCHW host data (diagnostics)."""

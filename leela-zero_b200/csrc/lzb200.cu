@@ -140,6 +140,10 @@ struct lzb_ctx {
     int* h_err = nullptr;  // pinned
     CUtensorMap tmV_first, tmV;
     long long launches = 0;
+    // per-launch timing (diagnostics): event pairs tagged with a kernel class
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_events;   // 2 per launch
+    std::vector<int> prof_class;
 };
 
 namespace {
@@ -178,16 +182,38 @@ int upload_transposed(float** dst, const float* src, int rows, int cols) {
 
 // ---- launches -------------------------------------------------------------
 
+enum KernelClass { kClassContraction = 0, kClassTransform = 1, kClassInput = 2, kClassHead = 3 };
+
+// Counts a launch and, while profiling, brackets it with two events.
+struct LaunchScope {
+    lzb_ctx* c;
+    LaunchScope(lzb_ctx* ctx, int cls) : c(ctx) {
+        c->launches++;
+        if (c->profiling) {
+            cudaEvent_t a, b;
+            cudaEventCreate(&a);
+            cudaEventCreate(&b);
+            c->prof_events.push_back(a);
+            c->prof_events.push_back(b);
+            c->prof_class.push_back(cls);
+            cudaEventRecord(a, c->stream);
+        }
+    }
+    ~LaunchScope() {
+        if (c->profiling) cudaEventRecord(c->prof_events.back(), c->stream);
+    }
+};
+
 template <typename T>
 int launch_gemm(lzb_ctx* c, const Layer& L, int P) {
     lzb_pipe* p = c->pipe;
-    if (p->precision == LZB_FP32) {
+    {
+        LaunchScope scope(c, kClassContraction);
         const dim3 grid(round_up(P, kSimtTile) / kSimtTile, p->Cp / kSimtTile, kPoints);
         gemm_f32_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const float*>(c->V),
                                                      static_cast<const float*>(L.U),
                                                      static_cast<float*>(c->M), c->Pa, L.cin_p, p->Cp);
     }
-    c->launches++;
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }
@@ -198,10 +224,12 @@ int launch_gemm_tc(lzb_ctx* c, const Layer& L, int P, bool first) {
     const int nblk = (P + tc::kBlockM - 1) / tc::kBlockM;
     const int items = kPoints * nblk;
     const int grid = items < p->sm_count ? items : p->sm_count;
-    tc::gemm_tc_kernel<T><<<grid, tc::kThreads, tc::kSmemBytes, c->stream>>>(
-        first ? c->tmV_first : c->tmV, L.tmU, static_cast<T*>(c->M), c->Pa, P, p->Cp,
-        L.cin_p / tc::kChunkK, nblk, c->d_err);
-    c->launches++;
+    {
+        LaunchScope scope(c, kClassContraction);
+        tc::gemm_tc_kernel<T><<<grid, tc::kThreads, tc::kSmemBytes, c->stream>>>(
+            first ? c->tmV_first : c->tmV, L.tmU, static_cast<T*>(c->M), c->Pa, P, p->Cp,
+            L.cin_p / tc::kChunkK, nblk, c->d_err);
+    }
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }
@@ -221,9 +249,11 @@ int launch_xform(lzb_ctx* c, const Layer& L, int nb, const T* R, T* X_out, T* V)
     lzb_pipe* p = c->pipe;
     const dim3 grid(p->Cp / kChanPerCta, nb);
     const size_t smem = (size_t)kBoardCells * 32 * 2 * sizeof(T);
-    xform_kernel<T><<<grid, kXformThreads, smem, c->stream>>>(
-        static_cast<const T*>(c->M), c->Pa, p->Cp, L.mean, L.invstd, R, X_out, V);
-    c->launches++;
+    {
+        LaunchScope scope(c, kClassTransform);
+        xform_kernel<T><<<grid, kXformThreads, smem, c->stream>>>(
+            static_cast<const T*>(c->M), c->Pa, p->Cp, L.mean, L.invstd, R, X_out, V);
+    }
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }
@@ -236,8 +266,10 @@ int run_tower(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* va
     T* V = static_cast<T*>(c->V);
     T* X = static_cast<T*>(c->X);
     int rc;
-    first_in_transform_kernel<T><<<(P + 7) / 8, 256, 0, c->stream>>>(in_dev, V, c->Pa, P);
-    c->launches++;
+    {
+        LaunchScope scope(c, kClassInput);
+        first_in_transform_kernel<T><<<(P + 7) / 8, 256, 0, c->stream>>>(in_dev, V, c->Pa, P);
+    }
     LZB_CUDA(cudaGetLastError());
     if ((rc = contraction<T>(c, p->layers[0], P, true))) return rc;
     if ((rc = launch_xform<T>(c, p->layers[0], nb, nullptr, X, p->blocks ? V : nullptr))) return rc;
@@ -251,9 +283,11 @@ int run_tower(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* va
         if ((rc = launch_xform<T>(c, l2, nb, X, X, last ? nullptr : V))) return rc;
     }
     const int cells = nb * kSq;
-    head_conv_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(X, p->head_w, p->Cp, cells, pol_dev,
-                                                                 val_dev);
-    c->launches++;
+    {
+        LaunchScope scope(c, kClassHead);
+        head_conv_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(X, p->head_w, p->Cp, cells,
+                                                                     pol_dev, val_dev);
+    }
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }
@@ -636,11 +670,18 @@ int lzb_ctx_forward_heads_device(lzb_ctx* c, const float* in_dev, int n, float s
     if (!policy_dev || !winrate_dev) return fail(LZB_ERR_ARG, "null buffer");
     if ((rc = lzb_ctx_forward_device(c, in_dev, n, c->d_pol, c->d_val))) return rc;
     const Heads& h = c->pipe->heads;
-    policy_head_kernel<<<n, 384, 0, c->stream>>>(c->d_pol, h.bn_pol_mean, h.bn_pol_invstd, h.ip_pol_wT,
-                                                 h.ip_pol_b, 1.0f / softmax_temp, policy_dev);
-    value_head_kernel<<<n, 256, 0, c->stream>>>(c->d_val, h.bn_val_mean, h.bn_val_invstd, h.ip1_val_wT,
-                                                h.ip1_val_b, h.ip2_val_w, h.ip2_val_b, winrate_dev);
-    c->launches += 2;
+    {
+        LaunchScope scope(c, kClassHead);
+        policy_head_kernel<<<n, 384, 0, c->stream>>>(c->d_pol, h.bn_pol_mean, h.bn_pol_invstd,
+                                                     h.ip_pol_wT, h.ip_pol_b, 1.0f / softmax_temp,
+                                                     policy_dev);
+    }
+    {
+        LaunchScope scope(c, kClassHead);
+        value_head_kernel<<<n, 256, 0, c->stream>>>(c->d_val, h.bn_val_mean, h.bn_val_invstd,
+                                                    h.ip1_val_wT, h.ip1_val_b, h.ip2_val_w,
+                                                    h.ip2_val_b, winrate_dev);
+    }
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }
@@ -661,6 +702,36 @@ int lzb_ctx_forward_heads(lzb_ctx* c, const float* in, int n, float softmax_temp
     LZB_CUDA(cudaMemcpyAsync(winrate, c->d_winrate, (size_t)n * sizeof(float),
                              cudaMemcpyDeviceToHost, c->stream));
     return lzb_ctx_sync(c);
+}
+
+int lzb_ctx_profile_begin(lzb_ctx* c) {
+    if (!c) return fail(LZB_ERR_ARG, "null context");
+    if (c->profiling) return fail(LZB_ERR_ARG, "profiling already on");
+    c->profiling = true;
+    return LZB_OK;
+}
+
+int lzb_ctx_profile_end(lzb_ctx* c, double* ms_by_class, long long* launches_by_class) {
+    if (!c || !ms_by_class || !launches_by_class) return fail(LZB_ERR_ARG, "null argument");
+    if (!c->profiling) return fail(LZB_ERR_ARG, "profiling is off");
+    c->profiling = false;
+    int rc = lzb_ctx_sync(c);
+    for (int k = 0; k < 4; k++) {
+        ms_by_class[k] = 0.0;
+        launches_by_class[k] = 0;
+    }
+    for (size_t i = 0; i < c->prof_class.size(); i++) {
+        float ms = 0.f;
+        if (rc == LZB_OK && cudaEventElapsedTime(&ms, c->prof_events[2 * i], c->prof_events[2 * i + 1]) == cudaSuccess) {
+            ms_by_class[c->prof_class[i]] += ms;
+            launches_by_class[c->prof_class[i]]++;
+        }
+        cudaEventDestroy(c->prof_events[2 * i]);
+        cudaEventDestroy(c->prof_events[2 * i + 1]);
+    }
+    c->prof_events.clear();
+    c->prof_class.clear();
+    return rc;
 }
 
 int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n, const float* residual,

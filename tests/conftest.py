@@ -19,7 +19,8 @@ def load_package():
     if "leela_zero_b200" in sys.modules:
         return sys.modules["leela_zero_b200"]
     path = os.path.join(ROOT, "leela-zero_b200", "__init__.py")
-    spec = importlib.util.spec_from_file_location("leela_zero_b200", path)
+    spec = importlib.util.spec_from_file_location(
+        "leela_zero_b200", path, submodule_search_locations=[os.path.dirname(path)])
     mod = importlib.util.module_from_spec(spec)
     sys.modules["leela_zero_b200"] = mod
     spec.loader.exec_module(mod)

@@ -1,0 +1,46 @@
+"""The C-ABI library loads without a GPU and exports what include/lzb200.h
+declares; compute entry points fail loudly when no B200 is present."""
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "lzb200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(lzb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(lzb):
+    assert _declared() == sorted(lzb.SYMBOLS)
+
+
+def test_library_exports_every_declared_symbol(lzb):
+    lib = lzb.lib()
+    missing = [s for s in _declared() if not hasattr(lib, s)]
+    assert not missing, missing
+
+
+def test_no_cpu_fallback(lzb):
+    """Without a CUDA device the library must refuse, not compute elsewhere."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(lzb.LzbError):
+        lzb.device_count()
+    net = lzb.weights.synthetic_network(1, 8, 1)
+    with pytest.raises(lzb.LzbError):
+        lzb.Pipe(net, "fp32")
+
+
+def test_product_does_not_touch_the_oracle():
+    """Nothing under the package may import, link or open the checker."""
+    pkg = os.path.join(ROOT, "leela-zero_b200")
+    for base, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                text = open(os.path.join(base, f), errors="ignore").read()
+                assert "oracle" not in text.lower(), os.path.join(base, f)
