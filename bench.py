@@ -38,6 +38,8 @@ FLOPS_DIRECT = (2 * 9 * 18 * FILTERS * 361 + 2 * BLOCKS * 2 * 9 * FILTERS * FILT
                 + 2 * FILTERS * 3 * 361 + 708072)
 # executed by one launch of the contraction kernel per position: 36 points x 25 tiles x C x K MACs
 FLOPS_GEMM_PER_POS = 2 * 36 * 25 * FILTERS * FILTERS
+# algorithmic FLOPs of one 3x3 layer per position as a direct convolution (C = K = 256)
+FLOPS_CONV_PER_POS = 2 * 9 * FILTERS * FILTERS * 361
 # DRAM traffic of one contraction launch (64 positions), from the committed ncu capture; None until measured
 GEMM_DRAM_BYTES_PER_LAUNCH = None
 
@@ -182,6 +184,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--precision", default=PRECISION,
+                    choices=["fp16", "bf16", "fp16-winograd", "bf16-winograd", "fp32"])
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -201,7 +205,7 @@ def main():
     pkg = load_package()
     W = pkg.weights
     net = W.synthetic_network(BLOCKS, FILTERS, WEIGHT_SEED)
-    pipe = pkg.Pipe(net, PRECISION, device=local)
+    pipe = pkg.Pipe(net, args.precision, device=local)
     B = args.batch
     ctx = pipe.context(B)
     if args.micro_batch:
@@ -276,9 +280,10 @@ def main():
         value = world * B / (ms_dev * 1e-3)
         e2e = world * B / (ms_e2e * 1e-3)
         g_ms, g_n = prof["contraction"]
-        micro = args.micro_batch or min(64, B)
-        # every contraction launch but the input layer's covers one micro-batch of tower work
-        flops_per_launch = FLOPS_GEMM_PER_POS * micro
+        winograd = args.precision != "fp16" and args.precision != "bf16"
+        micro = args.micro_batch or (min(64, B) if winograd else B)
+        # every contraction launch but the input layer's covers one micro-batch of one tower layer
+        flops_per_launch = (FLOPS_GEMM_PER_POS if winograd else FLOPS_CONV_PER_POS) * micro
         avg_s = (g_ms / max(g_n, 1)) * 1e-3
         achieved = flops_per_launch / avg_s / 1e12 if avg_s > 0 else 0.0
         peak = peaks["bf16_tflops_sustained"]
@@ -287,7 +292,7 @@ def main():
             "metric": "positions/sec", "value": value, "unit": "positions/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+            "dtype": args.precision + " operands, f32 accumulate", "data": "synthetic",
             "config": {"workload": "config 3: 40 blocks x 256 filters, %d positions per GPU per step, "
                                    "tower + 1x1 head convs + policy/value heads on device" % B,
                        "blocks": BLOCKS, "filters": FILTERS, "batch_per_gpu": B,
@@ -304,7 +309,8 @@ def main():
                 "frac_of_burst_peak": value * FLOPS_DIRECT / 1e12 / peaks["bf16_tflops"],
                 "frac_of_sustained_peak": value * FLOPS_DIRECT / 1e12 / peaks["bf16_tflops_sustained"],
                 "per_gpu_tflops": value * FLOPS_DIRECT / 1e12 / world},
-            "roofline": {"kernel": "gemm_tc_kernel (36 channel contractions, tcgen05)",
+            "roofline": {"kernel": ("gemm_tc_kernel (36 Winograd channel contractions, tcgen05)" if winograd
+                                    else "conv_direct_kernel (3x3 conv + BN + residual + ReLU, implicit GEMM on tcgen05)"),
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
                          "flops_per_launch": flops_per_launch, "avg_launch_ms": avg_s * 1e3,

@@ -30,10 +30,23 @@ extern "C" {
 #define LZB_ERR_DEVICE_WAIT 3 /* a kernel gave up a bounded wait (see error text) */
 #define LZB_ERR_NOMEM 4
 
-/* Arithmetic of the residual tower. */
-#define LZB_FP32 0   /* fp32 storage, FFMA contraction                            */
-#define LZB_FP16 1   /* fp16 operands on tcgen05, fp32 accumulation               */
-#define LZB_BF16 2   /* bf16 operands on tcgen05, fp32 accumulation               */
+/*
+ * Arithmetic of the residual tower.
+ *  LZB_FP32            Winograd F(4x4,3x3), fp32 storage, FFMA contractions: the
+ *                      mode that reproduces CPUPipe to 1e-4.
+ *  LZB_FP16, LZB_BF16  16-bit operands on the tensor cores (tcgen05), fp32
+ *                      accumulation; each 3x3 layer is one implicit-GEMM
+ *                      convolution with batch-norm/residual/ReLU in its epilogue.
+ *  LZB_*_WINOGRAD      16-bit operands on the tensor cores through the Winograd
+ *                      pipeline (transform, 36 batched contractions, fused
+ *                      output/input transform).  3.6x fewer multiply-adds, about
+ *                      4x the rounding error of the direct form.
+ */
+#define LZB_FP32 0
+#define LZB_FP16 1
+#define LZB_BF16 2
+#define LZB_FP16_WINOGRAD 3
+#define LZB_BF16_WINOGRAD 4
 
 #define LZB_INPUT_PLANES 18
 #define LZB_SQ 361

@@ -1,0 +1,380 @@
+// 3x3 convolution + batch-norm + residual + ReLU as ONE implicit GEMM on the
+// Blackwell tensor cores (tcgen05, accumulators in tensor memory, operands
+// brought in by TMA), fp16 or bf16 operands with fp32 accumulation.
+//
+// Activation layout ("padded cell-major"): a position is stored as 20 rows of
+// 20 cells, row 0 and column 0 being zero halo; because rows and positions
+// follow each other without gaps, the halo of one row/position doubles as the
+// opposite halo of its neighbour:
+//     cell(n, y, x) = (n * 20 + y + 1) * 20 + (x + 1),  y, x in [0, 19)
+//     X[cell][Cp], channels innermost; Q = (20 * n + 1) * 20 cells in all.
+// With that layout the input of filter tap (dy, dx) for the 128 consecutive
+// output cells m0 .. m0+127 is simply rows m0 + 20*dy + dx .. of X, i.e. one
+// TMA box load at a shifted row coordinate (rows outside [0, Qa) read as zero).
+// Halo cells are computed like any other row and forced to zero on store, so
+// the output is again a valid input.
+//
+// GEMM view per output tile:  D[128 cells][Kp] = sum over 9 taps and Cin/64
+// chunks of A[128][64] * W[tap][Kp][64]^T.  Weights are stored
+// Wd[9][Kp][Cin] (input channel innermost), so both operands are K-major.
+//
+// Roles in the CTA (6 warps, one CTA per SM, persistent over a contiguous
+// range of tiles): warp 0 TMA producer, warp 1 MMA issuer and tensor-memory
+// owner, warps 2-5 epilogue.  Two 256-column accumulators alternate, so the
+// epilogue of tile i (tcgen05.ld, batch-norm, residual, ReLU, fp16 store)
+// overlaps the MMAs of tile i+1.  All waits are bounded (see mbar_wait).
+//
+// The arithmetic is that of CPUPipe's convolve3 + batchnorm
+// (src/CPUPipe.cpp:286-299, 352-377) evaluated directly instead of through
+// the Winograd transforms; it replaces the reference's three launches per
+// layer (src/OpenCL.cpp:332-494) with one.
+#pragma once
+#include "gemm_tcgen05.cuh"
+#include "winograd_math.cuh"
+
+namespace lzb {
+namespace dc {
+
+using namespace tc;   // PTX helpers, descriptor builders
+
+constexpr int kCellsPerRow = 20;
+constexpr int kCellsPerPos = 400;
+constexpr int kTileM = 128;
+constexpr int kDStages = 4;
+constexpr uint32_t kAStageBytes = kTileM * 128;            // 16 KB
+constexpr uint32_t kBStageBytes = kMaxN * 128;             // 32 KB
+constexpr uint32_t kDStageBytes = kAStageBytes + kBStageBytes;
+constexpr uint32_t kDSmemBytes = kDStages * kDStageBytes + 2 * kMaxN * 4 /* bn */ + kBarBytes + 1024;
+
+constexpr int kErrDcProducer = 201;
+constexpr int kErrDcMmaAcc = 202;
+constexpr int kErrDcMmaFull = 203;
+constexpr int kErrDcEpilogue = 204;
+
+__host__ __device__ inline long long cells_for(int n) { return (20LL * n + 1) * kCellsPerRow; }
+__host__ __device__ inline int cell_of(int n, int y, int x) {
+    return (n * 20 + y + 1) * kCellsPerRow + x + 1;
+}
+__device__ __forceinline__ bool cell_is_interior(int q, int Q) {
+    const int c = q % kCellsPerRow, r = (q / kCellsPerRow) % 20;
+    return q < Q && c != 0 && r != 0;
+}
+
+template <typename T> struct Vec2;
+template <> struct Vec2<__half> {
+    static __device__ __forceinline__ float2 unpack(uint32_t u) {
+        return __half22float2(*reinterpret_cast<__half2*>(&u));
+    }
+};
+template <> struct Vec2<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 unpack(uint32_t u) {
+        return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+    }
+};
+
+// tmX : 2-D map over the input activations [Qa rows][Cin], box 64 x 128.
+// tmW : 2-D map over this layer's weights  [9*Kp rows][Cin], box 64 x Kp.
+// out : output activations [Qa][Kp];  res : residual [Qa][Kp] or nullptr (may equal out).
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1) conv_direct_kernel(
+    const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+    T* out, const T* res, const float* __restrict__ bn_mean, const float* __restrict__ bn_invstd,
+    int Q, int Kp, int kchunks, int ntiles, int* err) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (base - raw);
+    float* s_mean = reinterpret_cast<float*>(smem + kDStages * kDStageBytes);
+    float* s_scale = s_mean + kMaxN;
+    unsigned char* bar_mem = smem + kDStages * kDStageBytes + 2 * kMaxN * 4;
+    const uint32_t bars = smem_u32(bar_mem);
+    auto full_bar = [&](int s) { return bars + 8u * (0 + s); };
+    auto empty_bar = [&](int s) { return bars + 8u * (4 + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (8 + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (10 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * 12);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 12 + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kDStages; i++) {
+            mbar_init(full_bar(i), 1);
+            mbar_init(empty_bar(i), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < Kp; i += blockDim.x) {
+        s_mean[i] = bn_mean[i];
+        s_scale[i] = bn_invstd[i];
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tile_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
+    const int tile_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
+    const int ksteps = 9 * kchunks;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            const uint32_t tx = kAStageBytes + static_cast<uint32_t>(Kp) * 128u;
+            for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
+                const int m0 = tile * kTileM;
+                for (int tap = 0; tap < 9 && ok; ++tap) {
+                    const int shift = (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
+                    for (int c = 0; c < kchunks; ++c) {
+                        ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, err, kErrDcProducer);
+                        if (!ok) break;
+                        const uint32_t sa = base + stage * kDStageBytes;
+                        mbar_expect_tx(full_bar(stage), tx);
+                        tma_load_2d(sa, &tmX, c * kChunkK, m0 + shift, full_bar(stage));
+                        tma_load_2d(sa + kAStageBytes, &tmW, c * kChunkK, tap * Kp, full_bar(stage));
+                        if (++stage == kDStages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (OperandFormat<T>::value << 7) |
+                                   (OperandFormat<T>::value << 10) |
+                                   (static_cast<uint32_t>(Kp >> 3) << 17) |
+                                   (static_cast<uint32_t>(kTileM >> 4) << 24);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int local = 0;
+            for (int tile = tile_begin; tile < tile_end && ok; ++tile, ++local) {
+                const int acc = local & 1;
+                const uint32_t accphase = (local >> 1) & 1u;
+                ok = mbar_wait(tempty_bar(acc), accphase ^ 1u, abort_flag, err, kErrDcMmaAcc);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kMaxN);
+                for (int ks = 0; ks < ksteps; ++ks) {
+                    ok = mbar_wait(full_bar(stage), phase, abort_flag, err, kErrDcMmaFull);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t sa = base + stage * kDStageBytes;
+                    const uint64_t a_desc = umma_desc_sw128(sa);
+                    const uint64_t b_desc = umma_desc_sw128(sa + kAStageBytes);
+#pragma unroll
+                    for (int k = 0; k < kChunkK / 16; ++k) {
+                        tcgen05_mma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                                        (ks > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty_bar(stage));
+                    if (++stage == kDStages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tcgen05_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        const int qd = warp & 3;
+        const T tag = T();
+        int local = 0;
+        for (int tile = tile_begin; tile < tile_end; ++tile, ++local) {
+            const int acc = local & 1;
+            const uint32_t accphase = (local >> 1) & 1u;
+            const int q = tile * kTileM + qd * 32 + lane;
+            const bool interior = cell_is_interior(q, Q);
+            const bool in_range = q < Q;
+            bool ok = mbar_wait(tfull_bar(acc), accphase, abort_flag, err, kErrDcEpilogue);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            T* orow = out + static_cast<size_t>(q) * Kp;
+            const T* rrow = res ? res + static_cast<size_t>(q) * Kp : nullptr;
+            const uint32_t taddr0 =
+                tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + static_cast<uint32_t>(acc * kMaxN);
+            for (int j = 0; j < Kp; j += 32) {
+                uint4 rv[4];
+                if (rrow && interior) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) rv[v] = reinterpret_cast<const uint4*>(rrow + j)[v];
+                }
+                uint32_t r[32];
+                LZB_TMEM_LD32(r, taddr0 + j);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (in_range) {
+                    uint4* dst = reinterpret_cast<uint4*>(orow + j);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint32_t o[4];
+                        const uint32_t rr[4] = {rv[v].x, rv[v].y, rv[v].z, rv[v].w};
+#pragma unroll
+                        for (int h = 0; h < 4; ++h) {
+                            const int col = j + 8 * v + 2 * h;
+                            // max(0, invstd * (x - mean) [+ residual]), src/CPUPipe.cpp:352-377
+                            float a = s_scale[col] * (__uint_as_float(r[8 * v + 2 * h]) - s_mean[col]);
+                            float b = s_scale[col + 1] * (__uint_as_float(r[8 * v + 2 * h + 1]) - s_mean[col + 1]);
+                            if (rrow && interior) {
+                                const float2 f = Vec2<T>::unpack(rr[h]);
+                                a += f.x;
+                                b += f.y;
+                            }
+                            a = interior ? fmaxf(a, 0.f) : 0.f;
+                            b = interior ? fmaxf(b, 0.f) : 0.f;
+                            o[h] = pack2(tag, a, b);
+                        }
+                        dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Helper kernels of the direct path (all bandwidth-trivial).
+// ---------------------------------------------------------------------------
+
+// Network input planes in[n][18][361] fp32 -> padded cell-major X0[Qa][64],
+// channels 18..63 and halo cells zero.  One thread per (cell, channel pair).
+template <typename T>
+__global__ void __launch_bounds__(256) input_to_cells_kernel(const float* __restrict__ in,
+                                                             T* __restrict__ X0, int n) {
+    using P2 = Pair<T>;
+    const long long total = cells_for(n) * 32;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int pair = static_cast<int>(i & 31);
+        const int q = static_cast<int>(i >> 5);
+        const int c = q % kCellsPerRow, r = q / kCellsPerRow;
+        float2 v = make_float2(0.f, 0.f);
+        if (c != 0 && (r % 20) != 0 && 2 * pair < kInputPlanes) {
+            const int pos = r / 20, y = r % 20 - 1, x = c - 1;
+            const float* src = in + ((size_t)pos * kInputPlanes + 2 * pair) * kSq + y * kBoard + x;
+            v = make_float2(src[0], src[kSq]);
+        }
+        *reinterpret_cast<typename P2::type*>(X0 + (size_t)q * 64 + 2 * pair) = P2::from_f2(v);
+    }
+}
+
+// Recover the 3x3 filters from their Winograd transform and lay them out for
+// the implicit GEMM:  U32[36][c_in][K] (U = G f G^T, src/Network.cpp:159-223)
+// -> Wd[9][Kp][Cin_p], zero padded.  f = P U P^T with P a left inverse of G:
+// rows 0 and 5 of G are unit vectors, and rows 1,2 differ only in the sign of
+// the middle coefficient, so f_0 = u_0, f_2 = u_5, f_1 = (u_2 - u_1) * 3/(2 sqrt 2).
+template <typename T>
+__global__ void untransform_u_kernel(const float* __restrict__ U32, T* __restrict__ Wd, int c_in,
+                                     int K, int Cin_p, int Kp) {
+    const int total = c_in * K;
+    const float mid = 3.0f / (2.0f * kSq2);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int k = i % K, c = i / K;
+        auto u = [&](int xi, int nu) { return U32[((size_t)(xi * 6 + nu) * c_in + c) * K + k]; };
+        float g[3][6];   // rows of P U
+        for (int nu = 0; nu < 6; nu++) {
+            g[0][nu] = u(0, nu);
+            g[1][nu] = (u(2, nu) - u(1, nu)) * mid;
+            g[2][nu] = u(5, nu);
+        }
+        for (int a = 0; a < 3; a++) {
+            const float f[3] = {g[a][0], (g[a][2] - g[a][1]) * mid, g[a][5]};
+            for (int b = 0; b < 3; b++) {
+                Wd[((size_t)(a * 3 + b) * Kp + k) * Cin_p + c] = (T)f[b];
+            }
+        }
+    }
+}
+
+// 1x1 head convolutions reading the padded cell-major layout (see
+// head_conv_kernel for the arithmetic).  One warp per board cell.
+template <typename T>
+__global__ void __launch_bounds__(256) head_conv_cells_kernel(
+    const T* __restrict__ X, const float* __restrict__ w, int Cp, int cells,
+    float* __restrict__ pol, float* __restrict__ val) {
+    using P2 = Pair<T>;
+    const int lane = threadIdx.x & 31;
+    const int cell = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (cell >= cells) return;
+    const int n = cell / kSq, s = cell % kSq;
+    const T* x = X + (size_t)cell_of(n, s / kBoard, s % kBoard) * Cp;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f;
+    for (int c = 2 * lane; c < Cp; c += 64) {
+        const float2 v = P2::to_f2(*reinterpret_cast<const typename P2::type*>(x + c));
+        const float2 w0 = *reinterpret_cast<const float2*>(w + c);
+        const float2 w1 = *reinterpret_cast<const float2*>(w + Cp + c);
+        const float2 w2 = *reinterpret_cast<const float2*>(w + 2 * Cp + c);
+        a0 += w0.x * v.x + w0.y * v.y;
+        a1 += w1.x * v.x + w1.y * v.y;
+        a2 += w2.x * v.x + w2.y * v.y;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        a0 += __shfl_xor_sync(0xffffffffu, a0, off);
+        a1 += __shfl_xor_sync(0xffffffffu, a1, off);
+        a2 += __shfl_xor_sync(0xffffffffu, a2, off);
+    }
+    if (lane == 0) {
+        pol[((size_t)n * 2 + 0) * kSq + s] = a0;
+        pol[((size_t)n * 2 + 1) * kSq + s] = a1;
+        val[(size_t)n * kSq + s] = a2;
+    }
+}
+
+// padded cell-major <-> fp32 NCHW (diagnostics)
+template <typename T>
+__global__ void nchw_to_cells_kernel(const float* __restrict__ src, T* __restrict__ dst, int n, int C,
+                                     int Cp) {
+    const long long total = cells_for(n) * Cp;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int ch = static_cast<int>(i % Cp);
+        const int q = static_cast<int>(i / Cp);
+        const int c = q % kCellsPerRow, r = q / kCellsPerRow;
+        float v = 0.f;
+        if (c != 0 && (r % 20) != 0 && ch < C) {
+            v = src[((size_t)(r / 20) * C + ch) * kSq + (r % 20 - 1) * kBoard + c - 1];
+        }
+        dst[i] = (T)v;
+    }
+}
+
+template <typename T>
+__global__ void cells_to_nchw_kernel(const T* __restrict__ src, float* __restrict__ dst, int n, int C,
+                                     int Cp) {
+    const size_t total = (size_t)n * C * kSq;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int s = i % kSq;
+        const int c = (i / kSq) % C;
+        const int b = i / ((size_t)C * kSq);
+        dst[i] = (float)src[(size_t)cell_of(b, s / kBoard, s % kBoard) * Cp + c];
+    }
+}
+
+}  // namespace dc
+}  // namespace lzb

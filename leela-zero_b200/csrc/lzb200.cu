@@ -22,6 +22,7 @@
 #include <string>
 #include <vector>
 
+#include "conv_direct.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
 #include "head_kernels.cuh"
@@ -100,6 +101,8 @@ struct Layer {
     int cin_p = 0;
     bool present = false;
     CUtensorMap tmU;
+    void* Wd = nullptr;         // direct path: [9][Kp][cin_p] storage type
+    CUtensorMap tmW;
 };
 
 struct Heads {
@@ -116,7 +119,8 @@ struct lzb_pipe {
     int channels = 0;   // C
     int Cp = 0;         // C rounded up to 64
     int blocks = 0;
-    int precision = LZB_FP16;
+    int precision = LZB_FP16;   // storage type: LZB_FP32, LZB_FP16 or LZB_BF16
+    bool direct = false;        // true: implicit-GEMM convolution; false: Winograd pipeline
     int elt = 2;        // bytes per stored element
     int sm_count = 0;
     std::vector<Layer> layers;
@@ -139,6 +143,10 @@ struct lzb_ctx {
     int* d_err = nullptr;
     int* h_err = nullptr;  // pinned
     CUtensorMap tmV_first, tmV;
+    // direct path: padded cell-major activations
+    int Qa = 0;            // rows allocated in IN / X / H
+    void *IN = nullptr, *H = nullptr;
+    CUtensorMap tmIN, tmX, tmH;
     long long launches = 0;
     // per-launch timing (diagnostics): event pairs tagged with a kernel class
     bool profiling = false;
@@ -155,6 +163,17 @@ int upload_layer_t(lzb_pipe* p, Layer& L, const float* U32_dev, int c_in) {
     const size_t n = (size_t)kPoints * p->Cp * L.cin_p;
     LZB_CUDA(cudaMalloc(&L.U, n * sizeof(T)));
     repack_u_kernel<T><<<1024, 256>>>(U32_dev, static_cast<T*>(L.U), c_in, p->channels, L.cin_p, p->Cp);
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+template <typename T>
+int upload_layer_direct_t(lzb_pipe* p, Layer& L, const float* U32_dev, int c_in) {
+    const size_t n = (size_t)9 * p->Cp * L.cin_p;
+    LZB_CUDA(cudaMalloc(&L.Wd, n * sizeof(T)));
+    LZB_CUDA(cudaMemset(L.Wd, 0, n * sizeof(T)));
+    dc::untransform_u_kernel<T><<<256, 256>>>(U32_dev, static_cast<T*>(L.Wd), c_in, p->channels,
+                                              L.cin_p, p->Cp);
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }
@@ -292,7 +311,58 @@ int run_tower(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* va
     return LZB_OK;
 }
 
+template <typename T>
+int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm_in, T* out,
+                       const T* res) {
+    lzb_pipe* p = c->pipe;
+    const int Q = static_cast<int>(dc::cells_for(nb));
+    const int ntiles = (Q + dc::kTileM - 1) / dc::kTileM;
+    const int grid = ntiles < p->sm_count ? ntiles : p->sm_count;
+    {
+        LaunchScope scope(c, kClassContraction);
+        dc::conv_direct_kernel<T><<<grid, tc::kThreads, dc::kDSmemBytes, c->stream>>>(
+            tm_in, L.tmW, out, res, L.mean, L.invstd, Q, p->Cp, L.cin_p / tc::kChunkK, ntiles,
+            c->d_err);
+    }
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+// One micro-batch through the tower, direct (implicit GEMM) path: one launch
+// per 3x3 layer, batch-norm / residual / ReLU in its epilogue.
+template <typename T>
+int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* val_dev) {
+    lzb_pipe* p = c->pipe;
+    T* X = static_cast<T*>(c->X);
+    T* H = static_cast<T*>(c->H);
+    int rc;
+    {
+        LaunchScope scope(c, kClassInput);
+        dc::input_to_cells_kernel<T><<<p->sm_count * 4, 256, 0, c->stream>>>(
+            in_dev, static_cast<T*>(c->IN), nb);
+    }
+    LZB_CUDA(cudaGetLastError());
+    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, X, nullptr))) return rc;
+    for (int b = 0; b < p->blocks; b++) {
+        if ((rc = launch_conv_direct<T>(c, p->layers[1 + 2 * b], nb, c->tmX, H, nullptr))) return rc;
+        if ((rc = launch_conv_direct<T>(c, p->layers[2 + 2 * b], nb, c->tmH, X, X))) return rc;
+    }
+    const int cells = nb * kSq;
+    {
+        LaunchScope scope(c, kClassHead);
+        dc::head_conv_cells_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(X, p->head_w, p->Cp, cells,
+                                                                              pol_dev, val_dev);
+    }
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
 int run_tower_any(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* val_dev) {
+    if (c->pipe->direct) {
+        return c->pipe->precision == LZB_FP16
+                   ? run_tower_direct<__half>(c, in_dev, nb, pol_dev, val_dev)
+                   : run_tower_direct<__nv_bfloat16>(c, in_dev, nb, pol_dev, val_dev);
+    }
     switch (c->pipe->precision) {
         case LZB_FP32: return run_tower<float>(c, in_dev, nb, pol_dev, val_dev);
         case LZB_FP16: return run_tower<__half>(c, in_dev, nb, pol_dev, val_dev);
@@ -331,6 +401,10 @@ int set_smem_attrs() {
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes));
     LZB_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<__nv_bfloat16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dc::conv_direct_kernel<__half>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc::kDSmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dc::conv_direct_kernel<__nv_bfloat16>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc::kDSmemBytes));
     return LZB_OK;
 }
 
@@ -338,6 +412,47 @@ int set_smem_attrs() {
 
 namespace {
 using namespace lzb;
+
+template <typename T>
+int debug_conv_direct_t(lzb_ctx* c, int layer, const float* in, int n, const float* residual,
+                        float* out) {
+    lzb_pipe* p = c->pipe;
+    const Layer& L = p->layers[layer];
+    const int C = p->channels;
+    const size_t plane_floats = (size_t)n * C * kSq;
+    const size_t in_floats = layer == 0 ? (size_t)n * LZB_IN_FLOATS : plane_floats;
+    float* stage = nullptr;
+    LZB_CUDA(cudaMalloc(&stage, sizeof(float) * (plane_floats > in_floats ? plane_floats : in_floats)));
+    int rc = LZB_OK;
+    auto guard = [&](cudaError_t e, const char* what) {
+        if (rc == LZB_OK && e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+    };
+    T* X = static_cast<T*>(c->X);
+    T* H = static_cast<T*>(c->H);
+    guard(cudaMemcpyAsync(stage, in, sizeof(float) * in_floats, cudaMemcpyHostToDevice, c->stream), "copy in");
+    if (layer == 0) {
+        dc::input_to_cells_kernel<T><<<512, 256, 0, c->stream>>>(stage, static_cast<T*>(c->IN), n);
+    } else {
+        dc::nchw_to_cells_kernel<T><<<512, 256, 0, c->stream>>>(stage, H, n, C, p->Cp);
+    }
+    const T* R = nullptr;
+    if (residual) {
+        guard(cudaMemcpyAsync(stage, residual, sizeof(float) * plane_floats, cudaMemcpyHostToDevice, c->stream), "copy residual");
+        dc::nchw_to_cells_kernel<T><<<512, 256, 0, c->stream>>>(stage, X, n, C, p->Cp);
+        R = X;
+    }
+    guard(cudaGetLastError(), "layout conversion");
+    if (rc == LZB_OK) rc = launch_conv_direct<T>(c, L, n, layer == 0 ? c->tmIN : c->tmH, X, R);
+    if (rc == LZB_OK) {
+        dc::cells_to_nchw_kernel<T><<<512, 256, 0, c->stream>>>(X, stage, n, C, p->Cp);
+        guard(cudaGetLastError(), "layout conversion");
+        guard(cudaMemcpyAsync(out, stage, sizeof(float) * plane_floats, cudaMemcpyDeviceToHost, c->stream), "copy out");
+    }
+    int rc2 = lzb_ctx_sync(c);
+    cudaFree(stage);
+    return rc ? rc : rc2;
+}
+
 template <typename T>
 int debug_conv_t(lzb_ctx* c, int layer, const float* in, int n, const float* residual, float* out) {
     lzb_pipe* p = c->pipe;
@@ -404,8 +519,13 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     if (!out) return fail(LZB_ERR_ARG, "null out");
     *out = nullptr;
     if (channels < 1 || blocks < 0) return fail(LZB_ERR_ARG, "bad channels/blocks");
-    if (precision != LZB_FP32 && precision != LZB_FP16 && precision != LZB_BF16) {
-        return fail(LZB_ERR_ARG, "unknown precision");
+    bool direct = false;
+    switch (precision) {
+        case LZB_FP32: break;
+        case LZB_FP16: case LZB_BF16: direct = true; break;
+        case LZB_FP16_WINOGRAD: precision = LZB_FP16; break;
+        case LZB_BF16_WINOGRAD: precision = LZB_BF16; break;
+        default: return fail(LZB_ERR_ARG, "unknown precision");
     }
     const int Cp = round_up(channels, 64);
     if (precision != LZB_FP32 && Cp > tc::kMaxN) {
@@ -426,6 +546,7 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     p->Cp = Cp;
     p->blocks = blocks;
     p->precision = precision;
+    p->direct = direct;
     p->elt = precision == LZB_FP32 ? 4 : 2;
     p->sm_count = prop.multiProcessorCount;
     p->layers.resize(1 + 2 * blocks);
@@ -438,6 +559,7 @@ void lzb_pipe_destroy(lzb_pipe* p) {
     cudaSetDevice(p->device);
     for (auto& L : p->layers) {
         cudaFree(L.U);
+        cudaFree(L.Wd);
         cudaFree(L.mean);
         cudaFree(L.invstd);
     }
@@ -467,6 +589,9 @@ int lzb_pipe_push_conv(lzb_pipe* p, int layer, const float* U, int c_in, const f
     int rc = LZB_OK;
     if (e != cudaSuccess) {
         rc = fail(LZB_ERR_CUDA, std::string("weight upload: ") + cudaGetErrorString(e));
+    } else if (p->direct) {
+        rc = p->precision == LZB_FP16 ? upload_layer_direct_t<__half>(p, L, U32, c_in)
+                                      : upload_layer_direct_t<__nv_bfloat16>(p, L, U32, c_in);
     } else if (p->precision == LZB_FP32) {
         rc = upload_layer_t<float>(p, L, U32, c_in);
     } else if (p->precision == LZB_FP16) {
@@ -482,7 +607,10 @@ int lzb_pipe_push_conv(lzb_pipe* p, int layer, const float* U, int c_in, const f
     if (rc) return rc;
     if ((rc = upload_padded(&L.mean, bn_mean, p->channels, p->Cp))) return rc;
     if ((rc = upload_padded(&L.invstd, bn_invstd, p->channels, p->Cp))) return rc;
-    if (p->precision != LZB_FP32) {
+    if (p->direct) {
+        rc = make_map_2d(&L.tmW, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p, p->Cp);
+        if (rc) return rc;
+    } else if (p->precision != LZB_FP32) {
         rc = make_map_2d(&L.tmU, p->precision, L.U, (uint64_t)kPoints * p->Cp, L.cin_p, p->Cp);
         if (rc) return rc;
     }
@@ -553,17 +681,27 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
     c->pipe = p;
     c->max_batch = max_batch;
     c->micro_cap = max_batch < kMaxMicroBatch ? max_batch : kMaxMicroBatch;
-    c->micro = c->micro_cap < kDefaultMicroBatch ? c->micro_cap : kDefaultMicroBatch;
-    c->Pa = round_up(c->micro_cap * kTilesPerPos, 128);
-    const size_t vm = (size_t)kPoints * c->Pa * p->Cp * p->elt;
     cudaError_t e = cudaSuccess;
     auto alloc = [&](void** ptr, size_t bytes) {
         if (e == cudaSuccess) e = cudaMalloc(ptr, bytes);
         if (e == cudaSuccess) e = cudaMemset(*ptr, 0, bytes);
     };
-    alloc(&c->V, vm);
-    alloc(&c->M, vm);
-    alloc(&c->X, (size_t)c->micro_cap * kSq * p->Cp * p->elt);
+    if (p->direct) {
+        // activations are small here (no transformed tensors): the whole batch
+        // goes through the tower in one piece by default
+        c->micro = c->micro_cap;
+        c->Qa = round_up(static_cast<int>(dc::cells_for(c->micro_cap)), dc::kTileM);
+        alloc(&c->IN, (size_t)c->Qa * 64 * p->elt);
+        alloc(&c->X, (size_t)c->Qa * p->Cp * p->elt);
+        alloc(&c->H, (size_t)c->Qa * p->Cp * p->elt);
+    } else {
+        c->micro = c->micro_cap < kDefaultMicroBatch ? c->micro_cap : kDefaultMicroBatch;
+        c->Pa = round_up(c->micro_cap * kTilesPerPos, 128);
+        const size_t vm = (size_t)kPoints * c->Pa * p->Cp * p->elt;
+        alloc(&c->V, vm);
+        alloc(&c->M, vm);
+        alloc(&c->X, (size_t)c->micro_cap * kSq * p->Cp * p->elt);
+    }
     alloc((void**)&c->d_in, (size_t)max_batch * LZB_IN_FLOATS * sizeof(float));
     alloc((void**)&c->d_pol, (size_t)max_batch * LZB_POL_FLOATS * sizeof(float));
     alloc((void**)&c->d_val, (size_t)max_batch * LZB_VAL_FLOATS * sizeof(float));
@@ -579,7 +717,15 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
         return code;
     }
     *c->h_err = 0;
-    if (p->precision != LZB_FP32) {
+    if (p->direct) {
+        int rc = make_map_2d(&c->tmIN, p->precision, c->IN, (uint64_t)c->Qa, 64, dc::kTileM);
+        if (!rc) rc = make_map_2d(&c->tmX, p->precision, c->X, (uint64_t)c->Qa, p->Cp, dc::kTileM);
+        if (!rc) rc = make_map_2d(&c->tmH, p->precision, c->H, (uint64_t)c->Qa, p->Cp, dc::kTileM);
+        if (rc) {
+            lzb_ctx_destroy(c);
+            return rc;
+        }
+    } else if (p->precision != LZB_FP32) {
         int rc = make_map_2d(&c->tmV_first, p->precision, c->V, (uint64_t)kPoints * c->Pa, 64, tc::kBlockM);
         if (!rc) rc = make_map_2d(&c->tmV, p->precision, c->V, (uint64_t)kPoints * c->Pa, p->Cp, tc::kBlockM);
         if (rc) {
@@ -598,7 +744,7 @@ void lzb_ctx_destroy(lzb_ctx* c) {
         cudaStreamSynchronize(c->stream);
         cudaStreamDestroy(c->stream);
     }
-    void* ptrs[] = {c->V, c->M, c->X, c->d_in, c->d_pol, c->d_val, c->d_policy, c->d_winrate, c->d_err};
+    void* ptrs[] = {c->V, c->M, c->X, c->IN, c->H, c->d_in, c->d_pol, c->d_val, c->d_policy, c->d_winrate, c->d_err};
     for (void* q : ptrs) cudaFree(q);
     if (c->h_err) cudaFreeHost(c->h_err);
     delete c;
@@ -606,7 +752,7 @@ void lzb_ctx_destroy(lzb_ctx* c) {
 
 int lzb_ctx_set_micro_batch(lzb_ctx* c, int positions) {
     if (!c) return fail(LZB_ERR_ARG, "null context");
-    if (positions == 0) positions = kDefaultMicroBatch;
+    if (positions == 0) positions = c->pipe->direct ? c->micro_cap : kDefaultMicroBatch;
     if (positions < 1) return fail(LZB_ERR_ARG, "bad micro-batch");
     c->micro = positions < c->micro_cap ? positions : c->micro_cap;
     return LZB_OK;
@@ -741,6 +887,11 @@ int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n, const floa
     if (layer < 0 || layer >= (int)c->pipe->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
     if (!in || !out) return fail(LZB_ERR_ARG, "null buffer");
     LZB_CUDA(cudaSetDevice(c->pipe->device));
+    if (c->pipe->direct) {
+        return c->pipe->precision == LZB_FP16
+                   ? debug_conv_direct_t<__half>(c, layer, in, n, residual, out)
+                   : debug_conv_direct_t<__nv_bfloat16>(c, layer, in, n, residual, out);
+    }
     switch (c->pipe->precision) {
         case LZB_FP32: return debug_conv_t<float>(c, layer, in, n, residual, out);
         case LZB_FP16: return debug_conv_t<__half>(c, layer, in, n, residual, out);
