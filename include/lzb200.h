@@ -187,6 +187,37 @@ int lzb_ctx_profile_end(lzb_ctx* c, double ms_by_class[4], long long launches_by
 int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n,
                        const float* residual, float* out);
 
+/*
+ * One 3x3 layer (Winograd F(4x4,3x3) in fp32, then batch-norm, optional
+ * residual, ReLU) that allocates nothing.  This entry point has no counterpart
+ * in the reference.
+ *
+ * Who needs it: a host that has given all device memory to its own pool at
+ * start-up, so that a later cudaMalloc inside this library would fail; and a
+ * thread that must not stall the rest of the process, since cudaMalloc and
+ * cudaFree synchronise the whole device.  Such callers cannot create a pipe
+ * or a context (both allocate), but they can still run a layer through this
+ * function: its working memory is a fixed array inside the library image
+ * (about 6 MB, held by every GPU that loads the library until the process
+ * ends), and inputs, weights and outputs are the caller's own DEVICE buffers.
+ *
+ * Limits: n <= 8 positions, c_in <= 64, channels <= 64; larger sizes are
+ * refused with LZB_ERR_ARG and an explanatory lzb_last_error().
+ * Arguments (all fp32, all on `device`): in [n][c_in][361]; U [36][c_in][channels]
+ * as for lzb_pipe_push_conv; bn_mean, bn_invstd [channels]; residual
+ * [n][channels][361] or NULL; out [n][channels][361].  The work is enqueued on
+ * `stream` (a cudaStream_t, NULL for the default stream) and not waited for.
+ *
+ * The first call on each device looks up the array's device address and sets
+ * kernel attributes; make that first call outside any stream capture.  All
+ * calls share the one array: it is rewritten (and cleared where needed) at the
+ * start of each call, and two calls whose kernels overlap on the GPU, from
+ * different streams or threads, race on it.  Serialise them.
+ */
+int lzb_conv3x3_static(int device, const float* in, int n, int c_in, int channels,
+                       const float* U, const float* bn_mean, const float* bn_invstd,
+                       const float* residual, float* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -28,6 +28,7 @@ SYMBOLS = (
     "lzb_ctx_forward_device", "lzb_ctx_forward_heads", "lzb_ctx_forward_heads_device",
     "lzb_ctx_sync", "lzb_ctx_stream", "lzb_ctx_set_micro_batch", "lzb_ctx_launch_count",
     "lzb_ctx_debug_conv", "lzb_ctx_profile_begin", "lzb_ctx_profile_end",
+    "lzb_conv3x3_static",
 )
 
 _f32p = ctypes.POINTER(ctypes.c_float)
@@ -70,6 +71,8 @@ def lib():
         L.lzb_ctx_debug_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
         L.lzb_ctx_profile_begin.argtypes = [vp]
         L.lzb_ctx_profile_end.argtypes = [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]
+        L.lzb_conv3x3_static.argtypes = [ctypes.c_int, vp, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                         vp, vp, vp, vp, vp, vp]
         _lib = L
     return _lib
 

@@ -850,6 +850,121 @@ int lzb_ctx_forward_heads(lzb_ctx* c, const float* in, int n, float softmax_temp
     return lzb_ctx_sync(c);
 }
 
+// ---------------------------------------------------------------------------
+// One 3x3 layer without any allocation (lzb_conv3x3_static).
+//
+// All working memory of this entry point lives in the array below, which is
+// part of the library image: every GPU that loads the library holds these
+// bytes until the process exits.  Limits: 8 positions, 64 input and 64 output
+// channels (fp32).  Layout of the array (offsets are multiples of 256 bytes):
+//   U   repacked filters   [36][64][64] fp32
+//   V   transformed input  [36][256][64] fp32
+//   M   contraction result [36][256][64] fp32
+//   X   activations        [8][361][64] fp32
+//   BN  mean[64], invstd[64]
+// ---------------------------------------------------------------------------
+constexpr int kStaticMaxBatch = 8;
+constexpr int kStaticMaxChannels = 64;
+constexpr int kStaticRows = 256;   // 8 * 25 = 200 tiles, rounded up to the contraction tile
+constexpr size_t kStaticU = 0;
+constexpr size_t kStaticV = kStaticU + (size_t)36 * 64 * 64 * 4;
+constexpr size_t kStaticM = kStaticV + (size_t)36 * kStaticRows * 64 * 4;
+constexpr size_t kStaticX = kStaticM + (size_t)36 * kStaticRows * 64 * 4;
+constexpr size_t kStaticBN = kStaticX + (size_t)kStaticMaxBatch * 361 * 64 * 4;
+constexpr size_t kStaticScratchBytes = kStaticBN + 2 * 64 * 4 + 256;
+static_assert(kStaticV % 256 == 0 && kStaticM % 256 == 0 && kStaticX % 256 == 0 && kStaticBN % 256 == 0,
+              "sub-buffers must keep the 256-byte alignment of the array");
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+std::mutex g_static_mutex;
+unsigned char* g_static_ptr[kStaticMaxDevices] = {};   // device address of the array, per device
+
+// Once per device, with that device current: ask the runtime where the array
+// lives on this GPU.  In host code the name g_static_scratch is only a handle
+// for the symbol, not an address a kernel could use.
+int static_scratch_for(int device, unsigned char** out) {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[device]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr) {
+            return fail(LZB_ERR_CUDA, std::string("cudaGetSymbolAddress(g_static_scratch): ") +
+                                          cudaGetErrorString(e));
+        }
+        e = cudaFuncSetAttribute(lzb::xform_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 lzb::kBoardCells * 32 * 2 * 4);
+        if (e == cudaSuccess) {
+            e = cudaFuncSetAttribute(lzb::in_transform_kernel<float>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     lzb::kBoardCells * 32 * 2 * 4);
+        }
+        if (e != cudaSuccess) {
+            return fail(LZB_ERR_CUDA, std::string("kernel attribute set-up: ") + cudaGetErrorString(e));
+        }
+        g_static_ptr[device] = static_cast<unsigned char*>(ptr);
+    }
+    *out = g_static_ptr[device];
+    return LZB_OK;
+}
+}  // namespace
+
+int lzb_conv3x3_static(int device, const float* in_dev, int n, int c_in, int channels,
+                       const float* U_dev, const float* bn_mean_dev, const float* bn_invstd_dev,
+                       const float* residual_dev, float* out_dev, void* stream_handle) {
+    using namespace lzb;
+    if (!in_dev || !U_dev || !bn_mean_dev || !bn_invstd_dev || !out_dev) {
+        return fail(LZB_ERR_ARG, "null device pointer");
+    }
+    if (device < 0 || device >= kStaticMaxDevices) return fail(LZB_ERR_ARG, "device ordinal out of range");
+    if (n < 1 || n > kStaticMaxBatch) {
+        return fail(LZB_ERR_ARG, "lzb_conv3x3_static handles 1.." + std::to_string(kStaticMaxBatch) +
+                                     " positions, got " + std::to_string(n));
+    }
+    if (c_in < 1 || c_in > kStaticMaxChannels || channels < 1 || channels > kStaticMaxChannels) {
+        return fail(LZB_ERR_ARG, "lzb_conv3x3_static handles at most " +
+                                     std::to_string(kStaticMaxChannels) + " input and output channels, got " +
+                                     std::to_string(c_in) + " and " + std::to_string(channels));
+    }
+    LZB_CUDA(cudaSetDevice(device));
+    unsigned char* scratch = nullptr;
+    int rc = static_scratch_for(device, &scratch);
+    if (rc) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    float* U = reinterpret_cast<float*>(scratch + kStaticU);
+    float* V = reinterpret_cast<float*>(scratch + kStaticV);
+    float* M = reinterpret_cast<float*>(scratch + kStaticM);
+    float* X = reinterpret_cast<float*>(scratch + kStaticX);
+    float* bn = reinterpret_cast<float*>(scratch + kStaticBN);
+    const int Cp = 64, P = n * kTilesPerPos;
+    // The array keeps whatever the previous call left.  Everything read below
+    // is rewritten first; the padded batch-norm entries are the one part a
+    // kernel does not rewrite, so they are cleared here.
+    LZB_CUDA(cudaMemsetAsync(bn, 0, 2 * 64 * sizeof(float), stream));
+    LZB_CUDA(cudaMemcpyAsync(bn, bn_mean_dev, channels * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+    LZB_CUDA(cudaMemcpyAsync(bn + 64, bn_invstd_dev, channels * sizeof(float), cudaMemcpyDeviceToDevice,
+                             stream));
+    repack_u_kernel<float><<<144, 256, 0, stream>>>(U_dev, U, c_in, channels, Cp, Cp);
+    nchw_to_nhwc_kernel<float><<<128, 256, 0, stream>>>(in_dev, X, n, c_in, Cp);
+    const dim3 tgrid(Cp / kChanPerCta, n);
+    const size_t tsmem = (size_t)kBoardCells * 32 * 2 * sizeof(float);
+    in_transform_kernel<float><<<tgrid, kXformThreads, tsmem, stream>>>(X, V, kStaticRows, Cp);
+    const dim3 ggrid(round_up(P, kSimtTile) / kSimtTile, Cp / kSimtTile, kPoints);
+    gemm_f32_kernel<<<ggrid, 256, 0, stream>>>(V, U, M, kStaticRows, Cp, Cp);
+    const float* R = nullptr;
+    if (residual_dev) {
+        nchw_to_nhwc_kernel<float><<<128, 256, 0, stream>>>(residual_dev, X, n, channels, Cp);
+        R = X;
+    }
+    xform_kernel<float><<<tgrid, kXformThreads, tsmem, stream>>>(M, kStaticRows, Cp, bn, bn + 64, R, X,
+                                                                  nullptr);
+    nhwc_to_nchw_kernel<float><<<128, 256, 0, stream>>>(X, out_dev, n, channels, Cp);
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
 int lzb_ctx_profile_begin(lzb_ctx* c) {
     if (!c) return fail(LZB_ERR_ARG, "null context");
     if (c->profiling) return fail(LZB_ERR_ARG, "profiling already on");
