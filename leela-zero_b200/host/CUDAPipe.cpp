@@ -1,0 +1,279 @@
+// CUDAPipe implementation: request queue, batch forming, per-GPU workers,
+// drain/resume.  See CUDAPipe.h for the contract and the reference lines.
+#include "CUDAPipe.h"
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <stdexcept>
+
+#include "lzb200.h"
+
+namespace {
+
+// Production backend: one lzb_pipe per GPU, one lzb_ctx per worker slot.
+class LzbBackend : public CUDAPipe::Backend {
+public:
+    ~LzbBackend() override {
+        for (auto& per_gpu : m_ctx)
+            for (auto* c : per_gpu) lzb_ctx_destroy(c);
+        for (auto* p : m_pipes) lzb_pipe_destroy(p);
+    }
+
+    void load(const std::vector<int>& gpus, int channels, int blocks, int max_batch,
+              int workers_per_gpu, CUDAPipe::Precision precision,
+              const ForwardPipe::ForwardPipeWeights& w) override {
+        for (int gpu : gpus) {
+            lzb_pipe* p = nullptr;
+            check(lzb_pipe_create(&p, gpu, channels, blocks, static_cast<int>(precision)));
+            m_pipes.push_back(p);
+            for (size_t l = 0; l < w.m_conv_weights.size(); l++) {
+                const int c_in = l == 0 ? LZB_INPUT_PLANES : channels;
+                check(lzb_pipe_push_conv(p, static_cast<int>(l), w.m_conv_weights[l].data(), c_in,
+                                         w.m_batchnorm_means[l].data(),
+                                         w.m_batchnorm_stddevs[l].data()));
+            }
+            check(lzb_pipe_push_head_convs(p, w.m_conv_pol_w.data(), w.m_conv_val_w.data()));
+            check(lzb_pipe_finalize(p));
+            m_ctx.emplace_back();
+            for (int s = 0; s < workers_per_gpu; s++) {
+                lzb_ctx* c = nullptr;
+                check(lzb_ctx_create(&c, p, max_batch));
+                m_ctx.back().push_back(c);
+            }
+        }
+    }
+
+    int forward(int gpu_index, int worker, const float* in, int n, float* pol, float* val,
+                std::string* error) override {
+        const int rc = lzb_ctx_forward(m_ctx[gpu_index][worker], in, n, pol, val);
+        if (rc != LZB_OK && error) *error = lzb_last_error();
+        return rc;
+    }
+
+private:
+    static void check(int rc) {
+        // Initialisation failures surface as std::runtime_error, as in the
+        // reference (src/OpenCL.cpp:809, 823, 871, 905).
+        if (rc != LZB_OK) throw std::runtime_error(std::string("CUDAPipe: ") + lzb_last_error());
+    }
+    std::vector<lzb_pipe*> m_pipes;
+    std::vector<std::vector<lzb_ctx*>> m_ctx;
+};
+
+}  // namespace
+
+CUDAPipe::CUDAPipe(std::vector<int> gpus, int batch_size, int num_threads, Precision precision)
+    : CUDAPipe(std::move(gpus), batch_size, num_threads, precision,
+               std::unique_ptr<Backend>(new LzbBackend)) {}
+
+CUDAPipe::CUDAPipe(std::vector<int> gpus, int batch_size, int num_threads, Precision precision,
+                   std::unique_ptr<Backend> backend)
+    : m_gpus(std::move(gpus)),
+      m_batch_size(std::max(1, batch_size)),
+      m_num_threads(std::max(1, num_threads)),
+      m_precision(precision),
+      m_backend(std::move(backend)) {
+    // An empty list means "pick one" in the engine (src/OpenCLScheduler.cpp:90-94).
+    if (m_gpus.empty()) m_gpus.push_back(0);
+}
+
+CUDAPipe::~CUDAPipe() {
+    {
+        std::lock_guard<std::mutex> lk(m_mutex);
+        m_running = false;
+    }
+    m_cv.notify_all();
+    for (auto& t : m_threads) t.join();
+    // Anyone still queued is released rather than left asleep.
+    std::deque<EntryPtr> left;
+    {
+        std::lock_guard<std::mutex> lk(m_mutex);
+        left.swap(m_queue);
+    }
+    for (auto& e : left) finish(e, true, "");
+}
+
+void CUDAPipe::initialize(int channels) {
+    // The tower depth is only known when the weights arrive, so the device
+    // side is built in push_weights; the call order is fixed by
+    // Network::init_net (src/Network.cpp:407-414).
+    m_channels = channels;
+}
+
+void CUDAPipe::push_weights(unsigned int /*filter_size*/, unsigned int /*channels*/,
+                            unsigned int outputs,
+                            std::shared_ptr<const ForwardPipeWeights> weights) {
+    if (!weights || weights->m_conv_weights.empty() || weights->m_conv_weights.size() % 2 == 0) {
+        throw std::runtime_error("CUDAPipe: malformed weights (expected 1 + 2*blocks layers)");
+    }
+    if (m_channels == 0) m_channels = static_cast<int>(outputs);
+    if (static_cast<int>(outputs) != m_channels) {
+        throw std::runtime_error("CUDAPipe: push_weights does not match initialize(channels)");
+    }
+    if (!m_threads.empty()) throw std::runtime_error("CUDAPipe: weights pushed twice");
+    const int blocks = static_cast<int>(weights->m_conv_weights.size() - 1) / 2;
+    // Same sizing rule as the reference: at least one worker per GPU, more when
+    // many search threads share few GPUs (src/OpenCLScheduler.cpp:113-114).
+    m_workers_per_gpu = m_num_threads / m_batch_size / (static_cast<int>(m_gpus.size()) + 1) + 1;
+    m_backend->load(m_gpus, m_channels, blocks, m_batch_size, m_workers_per_gpu, m_precision,
+                    *weights);
+    m_live_gpus = static_cast<int>(m_gpus.size());
+    m_gpu_failed.assign(m_gpus.size(), 0);
+    for (size_t g = 0; g < m_gpus.size(); g++) {
+        for (int s = 0; s < m_workers_per_gpu; s++) {
+            m_threads.emplace_back(&CUDAPipe::worker, this, static_cast<int>(g), s);
+        }
+    }
+}
+
+void CUDAPipe::finish(const EntryPtr& e, bool halted, const std::string& error) {
+    {
+        std::lock_guard<std::mutex> lk(e->mutex);
+        e->done = true;
+        e->halted = halted;
+        e->error = error;
+    }
+    e->cv.notify_all();
+}
+
+void CUDAPipe::forward(const std::vector<float>& input, std::vector<float>& output_pol,
+                       std::vector<float>& output_val) {
+    if (input.size() != static_cast<size_t>(kInputFloats) ||
+        output_pol.size() != static_cast<size_t>(kPolicyFloats) ||
+        output_val.size() != static_cast<size_t>(kValueFloats)) {
+        throw std::runtime_error("CUDAPipe::forward: wrong buffer sizes");
+    }
+    auto entry = std::make_shared<Entry>(input, output_pol, output_val);
+    {
+        std::lock_guard<std::mutex> lk(m_mutex);
+        if (m_draining) throw NetworkHaltException();
+        if (m_live_gpus.load() == 0) throw std::runtime_error("CUDAPipe: no GPU left in service");
+        m_queue.push_back(entry);
+        // Requests arriving while a partial batch is in flight mean the wait
+        // was too short (src/OpenCLScheduler.cpp:267-269).
+        if (m_partial_in_progress.load()) m_wait_ms += 2;
+    }
+    m_cv.notify_one();
+    std::unique_lock<std::mutex> lk(entry->mutex);
+    entry->cv.wait(lk, [&] { return entry->done; });
+    if (entry->halted) throw NetworkHaltException();
+    if (!entry->error.empty()) throw std::runtime_error("CUDAPipe: " + entry->error);
+}
+
+// Batch-forming heuristic of the reference (src/OpenCLScheduler.cpp:293-353):
+// wait up to m_wait_ms for a full batch; if it does not fill and no other
+// partial batch is in flight, send what is there and wait 1 ms less next time.
+std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out) {
+    std::vector<EntryPtr> batch;
+    *timed_out = false;
+    std::unique_lock<std::mutex> lk(m_mutex);
+    size_t count = 0;
+    while (true) {
+        if (!m_running) return batch;
+        count = m_queue.size();
+        if (count >= static_cast<size_t>(m_batch_size)) {
+            count = m_batch_size;
+            break;
+        }
+        const bool filled = m_cv.wait_for(lk, std::chrono::milliseconds(m_wait_ms), [this] {
+            return !m_running || m_queue.size() >= static_cast<size_t>(m_batch_size);
+        });
+        if (!m_running) return batch;
+        if (!filled && !m_queue.empty() && !m_partial_in_progress.exchange(true)) {
+            if (m_wait_ms > 1) m_wait_ms--;
+            count = std::min(m_queue.size(), static_cast<size_t>(m_batch_size));
+            *timed_out = true;
+            break;
+        }
+    }
+    batch.assign(m_queue.begin(), m_queue.begin() + count);
+    m_queue.erase(m_queue.begin(), m_queue.begin() + count);
+    return batch;
+}
+
+void CUDAPipe::worker(int gpu_index, int slot) {
+    std::vector<float> in(static_cast<size_t>(m_batch_size) * kInputFloats);
+    std::vector<float> pol(static_cast<size_t>(m_batch_size) * kPolicyFloats);
+    std::vector<float> val(static_cast<size_t>(m_batch_size) * kValueFloats);
+    while (true) {
+        {
+            std::lock_guard<std::mutex> lk(m_mutex);
+            if (m_gpu_failed[gpu_index]) return;   // a sibling worker saw this GPU fail
+        }
+        bool timed_out = false;
+        auto batch = pickup(&timed_out);
+        if (batch.empty()) return;   // shutting down
+        const int n = static_cast<int>(batch.size());
+        for (int i = 0; i < n; i++) {
+            std::memcpy(&in[static_cast<size_t>(i) * kInputFloats], batch[i]->in.data(),
+                        sizeof(float) * kInputFloats);
+        }
+        std::string error;
+        const int rc = m_backend->forward(gpu_index, slot, in.data(), n, pol.data(), val.data(), &error);
+        if (rc == 0) {
+            for (int i = 0; i < n; i++) {
+                std::memcpy(batch[i]->out_p.data(), &pol[static_cast<size_t>(i) * kPolicyFloats],
+                            sizeof(float) * kPolicyFloats);
+                std::memcpy(batch[i]->out_v.data(), &val[static_cast<size_t>(i) * kValueFloats],
+                            sizeof(float) * kValueFloats);
+            }
+        } else if (error.empty()) {
+            error = "backend error " + std::to_string(rc);
+        }
+        {
+            std::lock_guard<std::mutex> lk(m_mutex);
+            m_stats.batches++;
+            m_stats.positions += n;
+            if (n == m_batch_size) m_stats.full_batches++;
+            if (timed_out) m_stats.timeouts++;
+        }
+        for (auto& e : batch) finish(e, false, rc == 0 ? std::string() : error);
+        if (timed_out) m_partial_in_progress = false;
+        if (rc != 0) {
+            // This GPU leaves the rotation (its other workers stop at their
+            // next turn).  If it was the last one, wake everybody who waits.
+            std::deque<EntryPtr> orphans;
+            {
+                std::lock_guard<std::mutex> lk(m_mutex);
+                if (!m_gpu_failed[gpu_index]) {
+                    m_gpu_failed[gpu_index] = 1;
+                    if (--m_live_gpus <= 0) {
+                        m_live_gpus = 0;
+                        orphans.swap(m_queue);
+                    }
+                }
+            }
+            for (auto& e : orphans) finish(e, false, "no GPU left in service (" + error + ")");
+            return;
+        }
+    }
+}
+
+void CUDAPipe::drain() {
+    // Wake every queued caller; each throws NetworkHaltException out of
+    // forward() (src/OpenCLScheduler.cpp:412-433).  Batches already on a GPU
+    // complete normally.
+    std::deque<EntryPtr> queued;
+    {
+        std::lock_guard<std::mutex> lk(m_mutex);
+        m_draining = true;
+        queued.swap(m_queue);
+    }
+    for (auto& e : queued) finish(e, true, "");
+}
+
+void CUDAPipe::resume() {
+    // Called after all search threads returned (src/OpenCLScheduler.cpp:436-441).
+    std::lock_guard<std::mutex> lk(m_mutex);
+    m_draining = false;
+}
+
+CUDAPipe::Stats CUDAPipe::stats() const {
+    std::lock_guard<std::mutex> lk(m_mutex);
+    Stats s = m_stats;
+    s.wait_ms = m_wait_ms;
+    return s;
+}
+
+int CUDAPipe::live_gpus() const { return m_live_gpus.load(); }

@@ -1,0 +1,129 @@
+// CUDAPipe: the engine-facing ForwardPipe implementation for B200.
+//
+// It takes the place of OpenCLScheduler<net_t> (src/OpenCLScheduler.h:50-118,
+// src/OpenCLScheduler.cpp:85-441): callers block in forward() with one
+// position each; worker threads, some per GPU, gather the waiting positions
+// into batches, run them through the lzb200 C ABI (a full network replica per
+// GPU, no data moves between GPUs) and wake the callers.  drain() makes every
+// queued caller throw NetworkHaltException; resume() re-opens the pipe.
+//
+// Differences from the OpenCL scheduler, on purpose:
+//  * a batch that did not fill within the wait time is sent as it is (all
+//    waiting positions, not one): the CUDA kernels take any batch size;
+//  * callers wait on a completion flag, so spurious wake-ups are harmless
+//    (the reference waits on the condition variable without a predicate,
+//    src/OpenCLScheduler.cpp:272);
+//  * a GPU whose backend call fails is taken out of rotation, the callers of
+//    that batch get std::runtime_error, the other GPUs keep serving;
+//  * nothing here calls exit().
+#ifndef LZB_CUDAPIPE_H
+#define LZB_CUDAPIPE_H
+
+#ifdef LZ_REFERENCE_TREE
+#include "ForwardPipe.h"
+#include "Network.h"   // NetworkHaltException
+#else
+#include "forward_pipe_iface.h"
+#endif
+
+#include <atomic>
+#include <condition_variable>
+#include <cstddef>
+#include <deque>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+class CUDAPipe : public ForwardPipe {
+public:
+    enum class Precision { FP32 = 0, FP16 = 1, BF16 = 2, FP16_WINOGRAD = 3, BF16_WINOGRAD = 4 };
+
+    // What runs a batch.  The production backend calls the lzb200 C ABI; tests
+    // substitute their own to exercise the scheduler without a GPU.
+    class Backend {
+    public:
+        virtual ~Backend() = default;
+        // Called once, from push_weights.  `gpus` are device ordinals.
+        virtual void load(const std::vector<int>& gpus, int channels, int blocks, int max_batch,
+                          int workers_per_gpu, Precision precision,
+                          const ForwardPipeWeights& weights) = 0;
+        // Evaluate n positions on (gpu index, worker slot).  in [n][18*361],
+        // pol [n][2*361], val [n][361].  Returns 0 or an error code and text.
+        virtual int forward(int gpu_index, int worker, const float* in, int n, float* pol,
+                            float* val, std::string* error) = 0;
+    };
+
+    struct Stats {
+        std::size_t batches = 0;        // backend calls
+        std::size_t positions = 0;      // positions evaluated
+        std::size_t full_batches = 0;   // calls that carried batch_size positions
+        std::size_t timeouts = 0;       // calls sent because the wait ran out
+        int wait_ms = 0;                // current wait for a full batch
+    };
+
+    // gpus: CUDA ordinals (empty = device 0), batch_size = cfg_batch_size,
+    // num_threads = cfg_num_threads (sizes the worker pool like the reference).
+    CUDAPipe(std::vector<int> gpus, int batch_size, int num_threads,
+             Precision precision = Precision::FP16);
+    CUDAPipe(std::vector<int> gpus, int batch_size, int num_threads, Precision precision,
+             std::unique_ptr<Backend> backend);
+    ~CUDAPipe() override;
+
+    void initialize(int channels) override;
+    void forward(const std::vector<float>& input, std::vector<float>& output_pol,
+                 std::vector<float>& output_val) override;
+    void push_weights(unsigned int filter_size, unsigned int channels, unsigned int outputs,
+                      std::shared_ptr<const ForwardPipeWeights> weights) override;
+    void drain() override;
+    void resume() override;
+
+    Stats stats() const;
+    int live_gpus() const;
+
+    static constexpr int kInputFloats = 18 * 361;
+    static constexpr int kPolicyFloats = 2 * 361;
+    static constexpr int kValueFloats = 361;
+
+private:
+    struct Entry {
+        const std::vector<float>& in;
+        std::vector<float>& out_p;
+        std::vector<float>& out_v;
+        std::mutex mutex;
+        std::condition_variable cv;
+        bool done = false;
+        bool halted = false;
+        std::string error;
+        Entry(const std::vector<float>& i, std::vector<float>& p, std::vector<float>& v)
+            : in(i), out_p(p), out_v(v) {}
+    };
+    using EntryPtr = std::shared_ptr<Entry>;
+
+    void worker(int gpu_index, int slot);
+    std::vector<EntryPtr> pickup(bool* timed_out);
+    static void finish(const EntryPtr& e, bool halted, const std::string& error);
+
+    std::vector<int> m_gpus;
+    int m_batch_size;
+    int m_num_threads;
+    Precision m_precision;
+    std::unique_ptr<Backend> m_backend;
+    int m_channels = 0;
+    int m_workers_per_gpu = 1;
+
+    mutable std::mutex m_mutex;
+    std::condition_variable m_cv;
+    std::deque<EntryPtr> m_queue;
+    bool m_running = true;
+    std::atomic<bool> m_draining{false};
+    std::atomic<bool> m_partial_in_progress{false};
+    int m_wait_ms = 10;                 // start with 10 ms, adapted like the reference
+    std::atomic<int> m_live_gpus{0};
+    std::vector<char> m_gpu_failed;     // per GPU, guarded by m_mutex
+    std::vector<std::thread> m_threads;
+    Stats m_stats;
+};
+
+#endif
