@@ -40,8 +40,8 @@ FLOPS_DIRECT = (2 * 9 * 18 * FILTERS * 361 + 2 * BLOCKS * 2 * 9 * FILTERS * FILT
 FLOPS_GEMM_PER_POS = 2 * 36 * 25 * FILTERS * FILTERS
 # algorithmic FLOPs of one 3x3 layer per position as a direct convolution (C = K = 256)
 FLOPS_CONV_PER_POS = 2 * 9 * FILTERS * FILTERS * 361
-# DRAM traffic of one contraction launch (64 positions), from the committed ncu capture; None until measured
-GEMM_DRAM_BYTES_PER_LAUNCH = None
+# DRAM traffic (read + write) of one conv_direct_kernel launch at 256 positions, from the committed ncu capture
+GEMM_DRAM_BYTES_PER_LAUNCH = 84.6e6   # mean of two captured launches (61 and 108 MB), profiles/conv_direct_kernel_40x256_batch256.md
 
 
 def load_package():

@@ -11,6 +11,11 @@
 // With that layout the input of filter tap (dy, dx) for the 128 consecutive
 // output cells m0 .. m0+127 is simply rows m0 + 20*dy + dx .. of X, i.e. one
 // TMA box load at a shifted row coordinate (rows outside [0, Qa) read as zero).
+// The nine shifted inputs of a tile overlap almost entirely, so the kernel
+// loads ONE window of 176 rows per 64-channel chunk and points the nine MMA
+// groups at row offsets inside it: under the 128-byte swizzle a K-major tile
+// is a linear array of 128-byte rows whose swizzle phase comes from the
+// address bits, so a descriptor may start at any row.
 // Halo cells are computed like any other row and forced to zero on store, so
 // the output is again a valid input.
 //
@@ -18,11 +23,18 @@
 // chunks of A[128][64] * W[tap][Kp][64]^T.  Weights are stored
 // Wd[9][Kp][Cin] (input channel innermost), so both operands are K-major.
 //
-// Roles in the CTA (6 warps, one CTA per SM, persistent over a contiguous
+// Per tile and chunk the producer brings one window (22 KB) and nine weight
+// tiles (32 KB each, 5-deep ring): 1.24 MB per tile instead of 1.73 MB with one
+// activation tile per tap.
+//
+// Roles in the CTA (10 warps, one CTA per SM, persistent over a contiguous
 // range of tiles): warp 0 TMA producer, warp 1 MMA issuer and tensor-memory
-// owner, warps 2-5 epilogue.  Two 256-column accumulators alternate, so the
-// epilogue of tile i (tcgen05.ld, batch-norm, residual, ReLU, fp16 store)
-// overlaps the MMAs of tile i+1.  All waits are bounded (see mbar_wait).
+// owner, warps 2-9 epilogue (two warps per tensor-memory lane quadrant, each
+// converting half of the output channels, with the tensor-memory and residual
+// loads of the next 32-column chunk in flight while the current one is
+// processed).  Two 256-column accumulators alternate, so the epilogue of tile i
+// (tcgen05.ld, batch-norm, residual, ReLU, fp16 store) overlaps the MMAs of
+// tile i+1.  All waits are bounded (see mbar_wait).
 //
 // The arithmetic is that of CPUPipe's convolve3 + batchnorm
 // (src/CPUPipe.cpp:286-299, 352-377) evaluated directly instead of through
@@ -40,11 +52,19 @@ using namespace tc;   // PTX helpers, descriptor builders
 constexpr int kCellsPerRow = 20;
 constexpr int kCellsPerPos = 400;
 constexpr int kTileM = 128;
-constexpr int kDStages = 4;
-constexpr uint32_t kAStageBytes = kTileM * 128;            // 16 KB
+constexpr int kDcThreads = 320;            // producer warp, MMA warp, 8 epilogue warps
+// Activation window: the 128 output cells of a tile plus the cells the 9 taps
+// reach (+-21 rows), padded to +-24 so that it starts on an 8-row swizzle atom.
+constexpr int kWinPad = 24;
+constexpr int kWinRows = kTileM + 2 * kWinPad;             // 176
+constexpr uint32_t kWinBytes = kWinRows * 128;             // 22 KB per 64-channel chunk
+constexpr int kWinBufs = 2;
+constexpr int kBStages = 5;                                // weight-tile ring
 constexpr uint32_t kBStageBytes = kMaxN * 128;             // 32 KB
-constexpr uint32_t kDStageBytes = kAStageBytes + kBStageBytes;
-constexpr uint32_t kDSmemBytes = kDStages * kDStageBytes + 2 * kMaxN * 4 /* bn */ + kBarBytes + 1024;
+constexpr uint32_t kOperandBytes = kWinBufs * kWinBytes + kBStages * kBStageBytes;
+constexpr uint32_t kStageOutBytes = 32 * 64;               // one epilogue warp: 32 cells x 32 channels
+constexpr uint32_t kDSmemBytes =
+    kOperandBytes + 8 * kStageOutBytes + 2 * kMaxN * 4 /* bn */ + kBarBytes + 1024;
 
 constexpr int kErrDcProducer = 201;
 constexpr int kErrDcMmaAcc = 202;
@@ -72,47 +92,129 @@ template <> struct Vec2<__nv_bfloat16> {
     }
 };
 
-// tmX : 2-D map over the input activations [Qa rows][Cin], box 64 x 128.
-// tmW : 2-D map over this layer's weights  [9*Kp rows][Cin], box 64 x Kp.
-// out : output activations [Qa][Kp];  res : residual [Qa][Kp] or nullptr (may equal out).
+// 64 bytes (32 channels) of the residual row, or zeros.
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1) conv_direct_kernel(
+__device__ __forceinline__ void load_residual(uint4 (&v)[4], const T* src, bool use) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        v[i] = use ? reinterpret_cast<const uint4*>(src)[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+// One 32-channel chunk of one output cell: max(0, x * invstd - mean * invstd
+// [+ residual]) (src/CPUPipe.cpp:352-377), halo cells forced to zero, packed
+// to 16 bits and written to this warp's staging tile (32 cells x 64 bytes,
+// 64-byte swizzle: 16-byte word v of row r sits at slot v ^ ((r >> 1) & 3),
+// which is both bank-conflict free and the layout the TMA store expects).
+template <typename T>
+__device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const uint4 (&rv)[4],
+                                               const float* s_scale, const float* s_bias,
+                                               bool use_res, bool interior, unsigned char* stg_row,
+                                               int lane) {
+    const T tag = T();
+    const float4* sc4 = reinterpret_cast<const float4*>(s_scale);
+    const float4* bi4 = reinterpret_cast<const float4*>(s_bias);
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        const float4 s0 = sc4[2 * v], s1 = sc4[2 * v + 1];
+        const float4 b0 = bi4[2 * v], b1 = bi4[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const float bi[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const uint32_t rr[4] = {rv[v].x, rv[v].y, rv[v].z, rv[v].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            float a = fmaf(__uint_as_float(r[8 * v + 2 * h]), sc[2 * h], bi[2 * h]);
+            float b = fmaf(__uint_as_float(r[8 * v + 2 * h + 1]), sc[2 * h + 1], bi[2 * h + 1]);
+            if (use_res) {
+                const float2 f = Vec2<T>::unpack(rr[h]);
+                a += f.x;
+                b += f.y;
+            }
+            a = interior ? fmaxf(a, 0.f) : 0.f;
+            b = interior ? fmaxf(b, 0.f) : 0.f;
+            o[h] = pack2(tag, a, b);
+        }
+        *reinterpret_cast<uint4*>(stg_row + ((v ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// Hand the warp's staging tile to the TMA engine: rows m .. m+31, channels
+// col .. col+31 of the output.  Every lane fences its shared-memory writes
+// towards the async proxy, one lane issues the store.
+__device__ __forceinline__ void store_staged_tile(const CUtensorMap* map, uint32_t stg, int col,
+                                                  int row, int lane) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+        asm volatile(
+            "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                reinterpret_cast<uint64_t>(map)),
+            "r"(col), "r"(row), "r"(stg)
+            : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+}
+// Before the staging tile is overwritten: the previous store must have read it.
+__device__ __forceinline__ void wait_staged_tile_read(int lane) {
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
+}
+
+// tmX : 2-D map over the input activations [Qa rows][Cin], box 64 x kWinRows.
+// tmW : 2-D map over this layer's weights  [9*Kp rows][Cin], box 64 x Kp.
+// tmO : 2-D map over the output activations [Qa rows][Kp], box 32 x 32, 64-byte swizzle.
+// res : residual [Qa][Kp] or nullptr (may be the output buffer: a warp reads the
+//       residual of a chunk before it stores that chunk).
+template <typename T>
+__global__ void __launch_bounds__(kDcThreads, 1) conv_direct_kernel(
     const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-    T* out, const T* res, const float* __restrict__ bn_mean, const float* __restrict__ bn_invstd,
+    const __grid_constant__ CUtensorMap tmO, const T* res, const float* __restrict__ bn_mean, const float* __restrict__ bn_invstd,
     int Q, int Kp, int kchunks, int ntiles, int* err) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (base - raw);
-    float* s_mean = reinterpret_cast<float*>(smem + kDStages * kDStageBytes);
-    float* s_scale = s_mean + kMaxN;
-    unsigned char* bar_mem = smem + kDStages * kDStageBytes + 2 * kMaxN * 4;
+    const uint32_t win_base = base;
+    const uint32_t b_base = base + kWinBufs * kWinBytes;
+    unsigned char* stage_out = smem + kOperandBytes;            // 8 x 2 KB, 1024-byte aligned
+    float* s_scale = reinterpret_cast<float*>(stage_out + 8 * kStageOutBytes);
+    float* s_bias = s_scale + kMaxN;
+    unsigned char* bar_mem = stage_out + 8 * kStageOutBytes + 2 * kMaxN * 4;
     const uint32_t bars = smem_u32(bar_mem);
-    auto full_bar = [&](int s) { return bars + 8u * (0 + s); };
-    auto empty_bar = [&](int s) { return bars + 8u * (4 + s); };
-    auto tfull_bar = [&](int a) { return bars + 8u * (8 + a); };
-    auto tempty_bar = [&](int a) { return bars + 8u * (10 + a); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * 12);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 12 + 8);
+    auto bfull_bar = [&](int s) { return bars + 8u * (0 + s); };
+    auto bempty_bar = [&](int s) { return bars + 8u * (8 + s); };
+    auto wfull_bar = [&](int w) { return bars + 8u * (16 + w); };
+    auto wempty_bar = [&](int w) { return bars + 8u * (18 + w); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (20 + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (22 + a); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * 24);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 24 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kDStages; i++) {
-            mbar_init(full_bar(i), 1);
-            mbar_init(empty_bar(i), 1);
+        for (int i = 0; i < kBStages; i++) {
+            mbar_init(bfull_bar(i), 1);
+            mbar_init(bempty_bar(i), 1);
+        }
+        for (int i = 0; i < kWinBufs; i++) {
+            mbar_init(wfull_bar(i), 1);
+            mbar_init(wempty_bar(i), 1);
         }
         for (int a = 0; a < 2; a++) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);
+            mbar_init(tempty_bar(a), 8);     // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    // batch norm as one FMA per element: y = x * invstd + (-mean * invstd)
     for (int i = threadIdx.x; i < Kp; i += blockDim.x) {
-        s_mean[i] = bn_mean[i];
         s_scale[i] = bn_invstd[i];
+        s_bias[i] = -bn_mean[i] * bn_invstd[i];
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -128,38 +230,42 @@ __global__ void __launch_bounds__(kThreads, 1) conv_direct_kernel(
 
     const int tile_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * ntiles / gridDim.x);
     const int tile_end = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * ntiles / gridDim.x);
-    const int ksteps = 9 * kchunks;
 
     if (warp == 0) {
+        // ------------------------------------------------ TMA producer
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, wb = 0;
+            uint32_t phase = 0, wphase = 0;
             bool ok = true;
-            const uint32_t tx = kAStageBytes + static_cast<uint32_t>(Kp) * 128u;
+            const uint32_t btx = static_cast<uint32_t>(Kp) * 128u;
             for (int tile = tile_begin; tile < tile_end && ok; ++tile) {
                 const int m0 = tile * kTileM;
-                for (int tap = 0; tap < 9 && ok; ++tap) {
-                    const int shift = (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
-                    for (int c = 0; c < kchunks; ++c) {
-                        ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, err, kErrDcProducer);
+                for (int c = 0; c < kchunks && ok; ++c) {
+                    ok = mbar_wait(wempty_bar(wb), wphase ^ 1u, abort_flag, err, kErrDcProducer);
+                    if (!ok) break;
+                    mbar_expect_tx(wfull_bar(wb), kWinBytes);
+                    tma_load_2d(win_base + wb * kWinBytes, &tmX, c * kChunkK, m0 - kWinPad, wfull_bar(wb));
+                    if (++wb == kWinBufs) { wb = 0; wphase ^= 1u; }
+                    for (int tap = 0; tap < 9; ++tap) {
+                        ok = mbar_wait(bempty_bar(stage), phase ^ 1u, abort_flag, err, kErrDcProducer);
                         if (!ok) break;
-                        const uint32_t sa = base + stage * kDStageBytes;
-                        mbar_expect_tx(full_bar(stage), tx);
-                        tma_load_2d(sa, &tmX, c * kChunkK, m0 + shift, full_bar(stage));
-                        tma_load_2d(sa + kAStageBytes, &tmW, c * kChunkK, tap * Kp, full_bar(stage));
-                        if (++stage == kDStages) { stage = 0; phase ^= 1u; }
+                        mbar_expect_tx(bfull_bar(stage), btx);
+                        tma_load_2d(b_base + stage * kBStageBytes, &tmW, c * kChunkK, tap * Kp,
+                                    bfull_bar(stage));
+                        if (++stage == kBStages) { stage = 0; phase ^= 1u; }
                     }
                 }
             }
         }
     } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = (1u << 4) | (OperandFormat<T>::value << 7) |
                                    (OperandFormat<T>::value << 10) |
                                    (static_cast<uint32_t>(Kp >> 3) << 17) |
                                    (static_cast<uint32_t>(kTileM >> 4) << 24);
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, wb = 0;
+            uint32_t phase = 0, wphase = 0;
             bool ok = true;
             int local = 0;
             for (int tile = tile_begin; tile < tile_end && ok; ++tile, ++local) {
@@ -169,81 +275,90 @@ __global__ void __launch_bounds__(kThreads, 1) conv_direct_kernel(
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kMaxN);
-                for (int ks = 0; ks < ksteps; ++ks) {
-                    ok = mbar_wait(full_bar(stage), phase, abort_flag, err, kErrDcMmaFull);
+                for (int c = 0; c < kchunks && ok; ++c) {
+                    ok = mbar_wait(wfull_bar(wb), wphase, abort_flag, err, kErrDcMmaFull);
                     if (!ok) break;
-                    tcgen05_fence_after();
-                    const uint32_t sa = base + stage * kDStageBytes;
-                    const uint64_t a_desc = umma_desc_sw128(sa);
-                    const uint64_t b_desc = umma_desc_sw128(sa + kAStageBytes);
+                    const uint32_t win = win_base + wb * kWinBytes;
+                    for (int tap = 0; tap < 9; ++tap) {
+                        ok = mbar_wait(bfull_bar(stage), phase, abort_flag, err, kErrDcMmaFull);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        // rows of the window this tap reads: (24 + 20*dy + dx) .. +127
+                        const int row0 = kWinPad + (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
+                        const uint64_t a_desc = umma_desc_sw128(win + static_cast<uint32_t>(row0) * 128u);
+                        const uint64_t b_desc = umma_desc_sw128(b_base + stage * kBStageBytes);
 #pragma unroll
-                    for (int k = 0; k < kChunkK / 16; ++k) {
-                        tcgen05_mma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
-                                        (ks > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < kChunkK / 16; ++k) {
+                            tcgen05_mma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                                            (c > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                        }
+                        tcgen05_commit(bempty_bar(stage));
+                        if (++stage == kBStages) { stage = 0; phase ^= 1u; }
                     }
-                    tcgen05_commit(empty_bar(stage));
-                    if (++stage == kDStages) { stage = 0; phase ^= 1u; }
+                    if (!ok) break;
+                    tcgen05_commit(wempty_bar(wb));      // window free once these MMAs retire
+                    if (++wb == kWinBufs) { wb = 0; wphase ^= 1u; }
                 }
                 if (!ok) break;
                 tcgen05_commit(tfull_bar(acc));
             }
         }
     } else {
-        const int qd = warp & 3;
-        const T tag = T();
+        // ------------------------------------------------ epilogue (warps 2..9)
+        const int qd = warp & 3;                 // tensor-memory lane quadrant of this warp
+        const int ncols = Kp >> 1;               // this warp converts half of the channels
+        const int col0 = ((warp - 2) >> 2) * ncols;
+        unsigned char* stg_ptr = stage_out + (warp - 2) * kStageOutBytes;
+        const uint32_t stg = smem_u32(stg_ptr);
+        unsigned char* stg_row = stg_ptr + lane * 64;
         int local = 0;
         for (int tile = tile_begin; tile < tile_end; ++tile, ++local) {
             const int acc = local & 1;
             const uint32_t accphase = (local >> 1) & 1u;
             const int q = tile * kTileM + qd * 32 + lane;
             const bool interior = cell_is_interior(q, Q);
-            const bool in_range = q < Q;
             bool ok = mbar_wait(tfull_bar(acc), accphase, abort_flag, err, kErrDcEpilogue);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tcgen05_fence_after();
-            T* orow = out + static_cast<size_t>(q) * Kp;
-            const T* rrow = res ? res + static_cast<size_t>(q) * Kp : nullptr;
-            const uint32_t taddr0 =
-                tmem_base + (static_cast<uint32_t>(qd * 32) << 16) + static_cast<uint32_t>(acc * kMaxN);
-            for (int j = 0; j < Kp; j += 32) {
-                uint4 rv[4];
-                if (rrow && interior) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) rv[v] = reinterpret_cast<const uint4*>(rrow + j)[v];
-                }
-                uint32_t r[32];
-                LZB_TMEM_LD32(r, taddr0 + j);
+            const bool use_res = (res != nullptr) && interior;
+            const T* rrow = res + static_cast<size_t>(q) * Kp + col0;
+            const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) +
+                                    static_cast<uint32_t>(acc * kMaxN + col0);
+            const int row0 = tile * kTileM + qd * 32;     // first cell of this warp's 32 rows
+            uint32_t ra[32], rb[32];
+            uint4 va[4], vb[4];
+            load_residual(va, rrow, use_res);
+            LZB_TMEM_LD32(ra, taddr0);
+            for (int j = 0; j < ncols; j += 64) {
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (in_range) {
-                    uint4* dst = reinterpret_cast<uint4*>(orow + j);
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint32_t o[4];
-                        const uint32_t rr[4] = {rv[v].x, rv[v].y, rv[v].z, rv[v].w};
-#pragma unroll
-                        for (int h = 0; h < 4; ++h) {
-                            const int col = j + 8 * v + 2 * h;
-                            // max(0, invstd * (x - mean) [+ residual]), src/CPUPipe.cpp:352-377
-                            float a = s_scale[col] * (__uint_as_float(r[8 * v + 2 * h]) - s_mean[col]);
-                            float b = s_scale[col + 1] * (__uint_as_float(r[8 * v + 2 * h + 1]) - s_mean[col + 1]);
-                            if (rrow && interior) {
-                                const float2 f = Vec2<T>::unpack(rr[h]);
-                                a += f.x;
-                                b += f.y;
-                            }
-                            a = interior ? fmaxf(a, 0.f) : 0.f;
-                            b = interior ? fmaxf(b, 0.f) : 0.f;
-                            o[h] = pack2(tag, a, b);
-                        }
-                        dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+                const bool more = j + 32 < ncols;
+                if (more) {
+                    load_residual(vb, rrow + j + 32, use_res);
+                    LZB_TMEM_LD32(rb, taddr0 + j + 32);
+                }
+                wait_staged_tile_read(lane);
+                epilogue_chunk<T>(ra, va, s_scale + col0 + j, s_bias + col0 + j, use_res, interior,
+                                  stg_row, lane);
+                store_staged_tile(&tmO, stg, col0 + j, row0, lane);
+                if (more) {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (j + 64 < ncols) {
+                        load_residual(va, rrow + j + 64, use_res);
+                        LZB_TMEM_LD32(ra, taddr0 + j + 64);
                     }
+                    wait_staged_tile_read(lane);
+                    epilogue_chunk<T>(rb, vb, s_scale + col0 + j + 32, s_bias + col0 + j + 32, use_res,
+                                      interior, stg_row, lane);
+                    store_staged_tile(&tmO, stg, col0 + j + 32, row0, lane);
                 }
             }
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
+        // the bulk stores of this warp must be complete before the CTA retires
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
 
     tcgen05_fence_before();

@@ -138,6 +138,9 @@ __device__ __forceinline__ void tcgen05_mma_f16(uint32_t d_tmem, uint64_t a_desc
 // (64 16-bit elements) under the 128-byte swizzle TMA writes: 8-row groups are
 // 1024 bytes apart (stride byte offset), the leading byte offset is unused for
 // swizzled K-major tiles and set to 1 unit, descriptor version 1 (sm_100).
+// The swizzle phase is taken from the address bits, so the start address may
+// be any 128-byte row of a 1024-byte-aligned tile (base-offset field 0), and
+// +32 bytes steps 16 elements along K.
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);   // start address, 16-byte units

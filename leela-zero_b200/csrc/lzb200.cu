@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -72,21 +73,23 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 2-D map over a row-major [rows][cols] matrix of 16-bit elements; box =
-// 64 columns (128 bytes) x box_rows, written to shared memory under the
-// 128-byte swizzle the UMMA descriptors expect.
+// 2-D map over a row-major [rows][cols] matrix of 16-bit elements.  Operand
+// maps use boxes of 64 columns (128 bytes) x box_rows under the 128-byte swizzle
+// the UMMA descriptors expect; the output maps of the convolution kernel use
+// 32 x 32 boxes under the 64-byte swizzle.
 int make_map_2d(CUtensorMap* map, int precision, void* base, uint64_t rows, uint64_t cols,
-                uint32_t box_rows) {
+                uint32_t box_rows, uint32_t box_cols = 64,
+                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(LZB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {64, box_rows};
+    const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt =
         precision == LZB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         return fail(LZB_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
@@ -146,7 +149,8 @@ struct lzb_ctx {
     // direct path: padded cell-major activations
     int Qa = 0;            // rows allocated in IN / X / H
     void *IN = nullptr, *H = nullptr;
-    CUtensorMap tmIN, tmX, tmH;
+    CUtensorMap tmIN, tmX, tmH;      // window loads
+    CUtensorMap tmXo, tmHo;          // 32 x 32 output stores
     long long launches = 0;
     // per-launch timing (diagnostics): event pairs tagged with a kernel class
     bool profiling = false;
@@ -312,16 +316,16 @@ int run_tower(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* va
 }
 
 template <typename T>
-int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm_in, T* out,
-                       const T* res) {
+int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm_in,
+                       const CUtensorMap& tm_out, const T* res) {
     lzb_pipe* p = c->pipe;
     const int Q = static_cast<int>(dc::cells_for(nb));
     const int ntiles = (Q + dc::kTileM - 1) / dc::kTileM;
     const int grid = ntiles < p->sm_count ? ntiles : p->sm_count;
     {
         LaunchScope scope(c, kClassContraction);
-        dc::conv_direct_kernel<T><<<grid, tc::kThreads, dc::kDSmemBytes, c->stream>>>(
-            tm_in, L.tmW, out, res, L.mean, L.invstd, Q, p->Cp, L.cin_p / tc::kChunkK, ntiles,
+        dc::conv_direct_kernel<T><<<grid, dc::kDcThreads, dc::kDSmemBytes, c->stream>>>(
+            tm_in, L.tmW, tm_out, res, L.mean, L.invstd, Q, p->Cp, L.cin_p / tc::kChunkK, ntiles,
             c->d_err);
     }
     LZB_CUDA(cudaGetLastError());
@@ -334,7 +338,6 @@ template <typename T>
 int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* val_dev) {
     lzb_pipe* p = c->pipe;
     T* X = static_cast<T*>(c->X);
-    T* H = static_cast<T*>(c->H);
     int rc;
     {
         LaunchScope scope(c, kClassInput);
@@ -342,10 +345,10 @@ int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, fl
             in_dev, static_cast<T*>(c->IN), nb);
     }
     LZB_CUDA(cudaGetLastError());
-    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, X, nullptr))) return rc;
+    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, c->tmXo, nullptr))) return rc;
     for (int b = 0; b < p->blocks; b++) {
-        if ((rc = launch_conv_direct<T>(c, p->layers[1 + 2 * b], nb, c->tmX, H, nullptr))) return rc;
-        if ((rc = launch_conv_direct<T>(c, p->layers[2 + 2 * b], nb, c->tmH, X, X))) return rc;
+        if ((rc = launch_conv_direct<T>(c, p->layers[1 + 2 * b], nb, c->tmX, c->tmHo, nullptr))) return rc;
+        if ((rc = launch_conv_direct<T>(c, p->layers[2 + 2 * b], nb, c->tmH, c->tmXo, X))) return rc;
     }
     const int cells = nb * kSq;
     {
@@ -442,7 +445,7 @@ int debug_conv_direct_t(lzb_ctx* c, int layer, const float* in, int n, const flo
         R = X;
     }
     guard(cudaGetLastError(), "layout conversion");
-    if (rc == LZB_OK) rc = launch_conv_direct<T>(c, L, n, layer == 0 ? c->tmIN : c->tmH, X, R);
+    if (rc == LZB_OK) rc = launch_conv_direct<T>(c, L, n, layer == 0 ? c->tmIN : c->tmH, c->tmXo, R);
     if (rc == LZB_OK) {
         dc::cells_to_nchw_kernel<T><<<512, 256, 0, c->stream>>>(X, stage, n, C, p->Cp);
         guard(cudaGetLastError(), "layout conversion");
@@ -718,9 +721,13 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
     }
     *c->h_err = 0;
     if (p->direct) {
-        int rc = make_map_2d(&c->tmIN, p->precision, c->IN, (uint64_t)c->Qa, 64, dc::kTileM);
-        if (!rc) rc = make_map_2d(&c->tmX, p->precision, c->X, (uint64_t)c->Qa, p->Cp, dc::kTileM);
-        if (!rc) rc = make_map_2d(&c->tmH, p->precision, c->H, (uint64_t)c->Qa, p->Cp, dc::kTileM);
+        int rc = make_map_2d(&c->tmIN, p->precision, c->IN, (uint64_t)c->Qa, 64, dc::kWinRows);
+        if (!rc) rc = make_map_2d(&c->tmX, p->precision, c->X, (uint64_t)c->Qa, p->Cp, dc::kWinRows);
+        if (!rc) rc = make_map_2d(&c->tmH, p->precision, c->H, (uint64_t)c->Qa, p->Cp, dc::kWinRows);
+        if (!rc) rc = make_map_2d(&c->tmXo, p->precision, c->X, (uint64_t)c->Qa, p->Cp, 32, 32,
+                                  CU_TENSOR_MAP_SWIZZLE_64B);
+        if (!rc) rc = make_map_2d(&c->tmHo, p->precision, c->H, (uint64_t)c->Qa, p->Cp, 32, 32,
+                                  CU_TENSOR_MAP_SWIZZLE_64B);
         if (rc) {
             lzb_ctx_destroy(c);
             return rc;
