@@ -1,0 +1,306 @@
+// The implicit-GEMM convolution of conv_direct.cuh on CTA PAIRS
+// (tcgen05 cta_group::2): two CTAs of a 2-CTA cluster work on 256 consecutive
+// output cells, 128 each.  Each CTA stages its own activation window and only
+// HALF of every weight tile (128 of the 256 output channels); one
+// tcgen05.mma.cta_group::2 of shape 256 x 256 x 16, issued by the leader CTA,
+// reads both halves, and each CTA's tensor memory receives the accumulators of
+// its own 128 cells.  Compared with one CTA per tile this halves the weight
+// bytes every SM pulls from L2 and writes to shared memory (16 KB instead of
+// 32 KB per k-step), which is what caps the single-CTA kernel.
+//
+// Protocol (leader = cluster rank 0):
+//  * "full" barriers (weight stage, activation window) live in the leader and
+//    expect one arrive.expect_tx from each CTA's producer; both CTAs' TMA loads
+//    complete their bytes on the leader's barrier (cp.async.bulk.tensor
+//    .cta_group::2).  Only the leader's MMA lane waits on them.
+//  * "empty" barriers and the accumulator-full barriers exist in both CTAs at
+//    the same shared-memory offset; the leader's tcgen05.commit arrives on both.
+//  * accumulator-empty barriers live in the leader and collect the 8 epilogue
+//    warps of each CTA (the follower's arrive remotely).
+// Everything else (window addressing, epilogue, bounded waits) is shared with
+// the single-CTA kernel.
+#pragma once
+#include "conv_direct.cuh"
+
+namespace lzb {
+namespace dc2 {
+
+using namespace tc;
+using namespace dc;
+
+constexpr int kPairM = 2 * kTileM;                         // 256 cells per CTA pair
+constexpr int kB2Stages = 10;                              // ring of half weight tiles
+constexpr uint32_t kB2StageBytes = (kMaxN / 2) * 128;      // 16 KB
+constexpr uint32_t kOperand2Bytes = kWinBufs * kWinBytes + kB2Stages * kB2StageBytes;
+constexpr uint32_t kD2SmemBytes =
+    kOperand2Bytes + 8 * kStageOutBytes + 2 * kMaxN * 4 + kBarBytes + 1024;
+
+constexpr int kErrD2Producer = 301;
+constexpr int kErrD2MmaAcc = 302;
+constexpr int kErrD2MmaFull = 303;
+constexpr int kErrD2Epilogue = 304;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t d;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(d) : "r"(smem_addr), "r"(rank));
+    return d;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// TMA load into THIS CTA's shared memory whose bytes complete on a barrier of the pair's leader.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(leader_bar)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                     uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive, once the pair's MMAs issued so far have retired, on the barrier at
+// this shared-memory offset in BOTH CTAs of the pair.
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+        "[%0], %1;" ::"r"(bar),
+        "h"(static_cast<uint16_t>(3))
+        : "memory");
+}
+
+// tmX : activations [Qa][Cin], box 64 x kWinRows.   tmW : weights [9*Kp][Cin], box 64 x Kp/2.
+// tmO : outputs [Qa][Kp], box 32 x 32, 64-byte swizzle.   npairs : 256-cell tiles covering Q.
+template <typename T>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_direct2_kernel(
+    const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
+    const __grid_constant__ CUtensorMap tmO, const T* res, const float* __restrict__ bn_mean,
+    const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int npairs, int* err) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* smem = smem_raw + (base - raw);
+    const uint32_t win_base = base;
+    const uint32_t b_base = base + kWinBufs * kWinBytes;
+    unsigned char* stage_out = smem + kOperand2Bytes;
+    float* s_scale = reinterpret_cast<float*>(stage_out + 8 * kStageOutBytes);
+    float* s_bias = s_scale + kMaxN;
+    unsigned char* bar_mem = stage_out + 8 * kStageOutBytes + 2 * kMaxN * 4;
+    const uint32_t bars = smem_u32(bar_mem);
+    auto bfull_bar = [&](int s) { return bars + 8u * (0 + s); };      // leader's are used
+    auto bempty_bar = [&](int s) { return bars + 8u * (16 + s); };    // both CTAs
+    auto wfull_bar = [&](int w) { return bars + 8u * (32 + w); };     // leader's
+    auto wempty_bar = [&](int w) { return bars + 8u * (34 + w); };    // both
+    auto tfull_bar = [&](int a) { return bars + 8u * (36 + a); };     // both
+    auto tempty_bar = [&](int a) { return bars + 8u * (38 + a); };    // leader's
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * 40);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 40 + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kB2Stages; i++) {
+            mbar_init(bfull_bar(i), 2);      // one arrive.expect_tx per CTA of the pair
+            mbar_init(bempty_bar(i), 1);
+        }
+        for (int i = 0; i < kWinBufs; i++) {
+            mbar_init(wfull_bar(i), 2);
+            mbar_init(wempty_bar(i), 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 16);    // 8 epilogue warps in each CTA
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    for (int i = threadIdx.x; i < Kp; i += blockDim.x) {
+        s_scale[i] = bn_invstd[i];
+        s_bias[i] = -bn_mean[i] * bn_invstd[i];
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(const_cast<uint32_t*>(tmem_slot))),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the peer's barriers are initialised before anyone signals them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int nclusters = gridDim.x >> 1, cid = blockIdx.x >> 1;
+    const int pair_begin = static_cast<int>(static_cast<long long>(cid) * npairs / nclusters);
+    const int pair_end = static_cast<int>(static_cast<long long>(cid + 1) * npairs / nclusters);
+    const int half_n = Kp >> 1;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            int stage = 0, wb = 0;
+            uint32_t phase = 0, wphase = 0;
+            bool ok = true;
+            const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
+            for (int pair = pair_begin; pair < pair_end && ok; ++pair) {
+                const int m0 = pair * kPairM + static_cast<int>(rank) * kTileM;
+                for (int c = 0; c < kchunks && ok; ++c) {
+                    ok = mbar_wait(wempty_bar(wb), wphase ^ 1u, abort_flag, err, kErrD2Producer);
+                    if (!ok) break;
+                    const uint32_t wf = map_to_cta(wfull_bar(wb), 0);
+                    mbar_expect_tx_cluster(wf, kWinBytes);
+                    tma_load_2d_pair(win_base + wb * kWinBytes, &tmX, c * kChunkK, m0 - kWinPad, wf);
+                    if (++wb == kWinBufs) { wb = 0; wphase ^= 1u; }
+                    for (int tap = 0; tap < 9; ++tap) {
+                        ok = mbar_wait(bempty_bar(stage), phase ^ 1u, abort_flag, err, kErrD2Producer);
+                        if (!ok) break;
+                        const uint32_t bf = map_to_cta(bfull_bar(stage), 0);
+                        mbar_expect_tx_cluster(bf, btx);
+                        tma_load_2d_pair(b_base + stage * kB2StageBytes, &tmW, c * kChunkK,
+                                         tap * Kp + static_cast<int>(rank) * half_n, bf);
+                        if (++stage == kB2Stages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            const uint32_t idesc = (1u << 4) | (OperandFormat<T>::value << 7) |
+                                   (OperandFormat<T>::value << 10) |
+                                   (static_cast<uint32_t>(Kp >> 3) << 17) |
+                                   (static_cast<uint32_t>(kPairM >> 4) << 24);
+            int stage = 0, wb = 0;
+            uint32_t phase = 0, wphase = 0;
+            bool ok = true;
+            int local = 0;
+            for (int pair = pair_begin; pair < pair_end && ok; ++pair, ++local) {
+                const int acc = local & 1;
+                const uint32_t accphase = (local >> 1) & 1u;
+                ok = mbar_wait(tempty_bar(acc), accphase ^ 1u, abort_flag, err, kErrD2MmaAcc);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kMaxN);
+                for (int c = 0; c < kchunks && ok; ++c) {
+                    ok = mbar_wait(wfull_bar(wb), wphase, abort_flag, err, kErrD2MmaFull);
+                    if (!ok) break;
+                    const uint32_t win = win_base + wb * kWinBytes;
+                    for (int tap = 0; tap < 9; ++tap) {
+                        ok = mbar_wait(bfull_bar(stage), phase, abort_flag, err, kErrD2MmaFull);
+                        if (!ok) break;
+                        tcgen05_fence_after();
+                        const int row0 = kWinPad + (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
+                        const uint64_t a_desc = umma_desc_sw128(win + static_cast<uint32_t>(row0) * 128u);
+                        const uint64_t b_desc = umma_desc_sw128(b_base + stage * kB2StageBytes);
+#pragma unroll
+                        for (int k = 0; k < kChunkK / 16; ++k) {
+                            tcgen05_mma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                                                 (c > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                        }
+                        tcgen05_commit_pair(bempty_bar(stage));
+                        if (++stage == kB2Stages) { stage = 0; phase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    tcgen05_commit_pair(wempty_bar(wb));
+                    if (++wb == kWinBufs) { wb = 0; wphase ^= 1u; }
+                }
+                if (!ok) break;
+                tcgen05_commit_pair(tfull_bar(acc));
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue (warps 2..9, both CTAs)
+        const int qd = warp & 3;
+        const int ncols = Kp >> 1;
+        const int col0 = ((warp - 2) >> 2) * ncols;
+        unsigned char* stg_ptr = stage_out + (warp - 2) * kStageOutBytes;
+        const uint32_t stg = smem_u32(stg_ptr);
+        unsigned char* stg_row = stg_ptr + lane * 64;
+        int local = 0;
+        for (int pair = pair_begin; pair < pair_end; ++pair, ++local) {
+            const int acc = local & 1;
+            const uint32_t accphase = (local >> 1) & 1u;
+            const int row0 = pair * kPairM + static_cast<int>(rank) * kTileM + qd * 32;
+            const int q = row0 + lane;
+            const bool interior = cell_is_interior(q, Q);
+            bool ok = mbar_wait(tfull_bar(acc), accphase, abort_flag, err, kErrD2Epilogue);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
+            const bool use_res = (res != nullptr) && interior;
+            const T* rrow = res + static_cast<size_t>(q) * Kp + col0;
+            const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) +
+                                    static_cast<uint32_t>(acc * kMaxN + col0);
+            uint32_t ra[32], rb[32];
+            uint4 va[4], vb[4];
+            load_residual(va, rrow, use_res);
+            LZB_TMEM_LD32(ra, taddr0);
+            for (int j = 0; j < ncols; j += 64) {
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const bool more = j + 32 < ncols;
+                if (more) {
+                    load_residual(vb, rrow + j + 32, use_res);
+                    LZB_TMEM_LD32(rb, taddr0 + j + 32);
+                }
+                wait_staged_tile_read(lane);
+                epilogue_chunk<T>(ra, va, s_scale + col0 + j, s_bias + col0 + j, use_res, interior,
+                                  stg_row, lane);
+                store_staged_tile(&tmO, stg, col0 + j, row0, lane);
+                if (more) {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (j + 64 < ncols) {
+                        load_residual(va, rrow + j + 64, use_res);
+                        LZB_TMEM_LD32(ra, taddr0 + j + 64);
+                    }
+                    wait_staged_tile_read(lane);
+                    epilogue_chunk<T>(rb, vb, s_scale + col0 + j + 32, s_bias + col0 + j + 32, use_res,
+                                      interior, stg_row, lane);
+                    store_staged_tile(&tmO, stg, col0 + j + 32, row0, lane);
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();      // neither CTA may retire while its peer can still touch it
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(kTmemCols)
+                     : "memory");
+    }
+}
+
+}  // namespace dc2
+}  // namespace lzb

@@ -24,6 +24,7 @@
 #include <vector>
 
 #include "conv_direct.cuh"
+#include "conv_direct2.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
 #include "head_kernels.cuh"
@@ -105,7 +106,8 @@ struct Layer {
     bool present = false;
     CUtensorMap tmU;
     void* Wd = nullptr;         // direct path: [9][Kp][cin_p] storage type
-    CUtensorMap tmW;
+    CUtensorMap tmW;            // box 64 x Kp   (one CTA per tile)
+    CUtensorMap tmW2;           // box 64 x Kp/2 (CTA pairs)
 };
 
 struct Heads {
@@ -124,6 +126,7 @@ struct lzb_pipe {
     int blocks = 0;
     int precision = LZB_FP16;   // storage type: LZB_FP32, LZB_FP16 or LZB_BF16
     bool direct = false;        // true: implicit-GEMM convolution; false: Winograd pipeline
+    bool pairs = false;         // direct path on CTA pairs (tcgen05 cta_group::2)
     int elt = 2;        // bytes per stored element
     int sm_count = 0;
     std::vector<Layer> layers;
@@ -320,6 +323,18 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
                        const CUtensorMap& tm_out, const T* res) {
     lzb_pipe* p = c->pipe;
     const int Q = static_cast<int>(dc::cells_for(nb));
+    if (p->pairs) {
+        const int npairs = (Q + dc2::kPairM - 1) / dc2::kPairM;
+        const int clusters = npairs < p->sm_count / 2 ? npairs : p->sm_count / 2;
+        {
+            LaunchScope scope(c, kClassContraction);
+            dc2::conv_direct2_kernel<T><<<2 * clusters, dc::kDcThreads, dc2::kD2SmemBytes, c->stream>>>(
+                tm_in, L.tmW2, tm_out, res, L.mean, L.invstd, Q, p->Cp, L.cin_p / tc::kChunkK, npairs,
+                c->d_err);
+        }
+        LZB_CUDA(cudaGetLastError());
+        return LZB_OK;
+    }
     const int ntiles = (Q + dc::kTileM - 1) / dc::kTileM;
     const int grid = ntiles < p->sm_count ? ntiles : p->sm_count;
     {
@@ -408,6 +423,10 @@ int set_smem_attrs() {
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc::kDSmemBytes));
     LZB_CUDA(cudaFuncSetAttribute(dc::conv_direct_kernel<__nv_bfloat16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc::kDSmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dc2::conv_direct2_kernel<__half>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dc2::conv_direct2_kernel<__nv_bfloat16>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
     return LZB_OK;
 }
 
@@ -550,6 +569,9 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     p->blocks = blocks;
     p->precision = precision;
     p->direct = direct;
+    // CTA pairs are the default; LZB_CONV_PAIRS=0 selects the one-CTA-per-tile
+    // kernel (kept as a cross-check and for diagnostics).
+    p->pairs = direct && !(getenv("LZB_CONV_PAIRS") != nullptr && atoi(getenv("LZB_CONV_PAIRS")) == 0);
     p->elt = precision == LZB_FP32 ? 4 : 2;
     p->sm_count = prop.multiProcessorCount;
     p->layers.resize(1 + 2 * blocks);
@@ -612,6 +634,7 @@ int lzb_pipe_push_conv(lzb_pipe* p, int layer, const float* U, int c_in, const f
     if ((rc = upload_padded(&L.invstd, bn_invstd, p->channels, p->Cp))) return rc;
     if (p->direct) {
         rc = make_map_2d(&L.tmW, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p, p->Cp);
+        if (!rc) rc = make_map_2d(&L.tmW2, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p, p->Cp / 2);
         if (rc) return rc;
     } else if (p->precision != LZB_FP32) {
         rc = make_map_2d(&L.tmU, p->precision, L.U, (uint64_t)kPoints * p->Cp, L.cin_p, p->Cp);

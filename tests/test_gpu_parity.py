@@ -302,6 +302,21 @@ def test_contexts_on_concurrent_threads(lzb, W):
         assert np.array_equal(got[i][1], want[1][8 * i:8 * i + 8])
 
 
+def test_single_cta_and_cta_pair_kernels_agree(lzb, W, monkeypatch):
+    """The implicit-GEMM convolution exists as a one-CTA-per-tile kernel and as
+    a CTA-pair (tcgen05 cta_group::2) kernel; both accumulate in the same order,
+    so their outputs are identical."""
+    net = W.synthetic_network(3, 128, 2057, calibrated=True)
+    x = W.synthetic_positions(37, 1057)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("LZB_CONV_PAIRS", flag)
+        pipe = lzb.Pipe(net, "fp16")
+        outs.append(pipe.context(37).forward(x))
+        pipe.close()
+    assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+
+
 def test_profile_counters(lzb, W):
     net = W.synthetic_network(2, 64, 2056)
     ctx = lzb.Pipe(net, "fp16").context(4)
