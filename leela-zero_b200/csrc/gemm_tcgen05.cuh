@@ -87,9 +87,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false if the CTA is aborting or the limit ran out.
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                       int* err, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int* err, int code) {
     const unsigned long long t0 = globaltimer_ns();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -102,6 +101,11 @@ __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile i
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* err, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, err, code);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,

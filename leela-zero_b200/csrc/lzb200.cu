@@ -325,7 +325,12 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
     const int Q = static_cast<int>(dc::cells_for(nb));
     if (p->pairs) {
         const int npairs = (Q + dc2::kPairM - 1) / dc2::kPairM;
-        const int clusters = npairs < p->sm_count / 2 ? npairs : p->sm_count / 2;
+        // Every CTA pair runs `rounds` tiles; use just enough pairs for that many
+        // rounds (400 tiles on 74 pairs need 6 rounds, which 67 pairs also do:
+        // the idle SMs leave their power budget to the busy ones).
+        const int max_clusters = p->sm_count / 2;
+        const int rounds = (npairs + max_clusters - 1) / max_clusters;
+        const int clusters = (npairs + rounds - 1) / rounds;
         {
             LaunchScope scope(c, kClassContraction);
             dc2::conv_direct2_kernel<T><<<2 * clusters, dc::kDcThreads, dc2::kD2SmemBytes, c->stream>>>(
@@ -336,7 +341,8 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
         return LZB_OK;
     }
     const int ntiles = (Q + dc::kTileM - 1) / dc::kTileM;
-    const int grid = ntiles < p->sm_count ? ntiles : p->sm_count;
+    const int tile_rounds = (ntiles + p->sm_count - 1) / p->sm_count;
+    const int grid = (ntiles + tile_rounds - 1) / tile_rounds;
     {
         LaunchScope scope(c, kClassContraction);
         dc::conv_direct_kernel<T><<<grid, dc::kDcThreads, dc::kDSmemBytes, c->stream>>>(
