@@ -41,7 +41,7 @@ FLOPS_GEMM_PER_POS = 2 * 36 * 25 * FILTERS * FILTERS
 # algorithmic FLOPs of one 3x3 layer per position as a direct convolution (C = K = 256)
 FLOPS_CONV_PER_POS = 2 * 9 * FILTERS * FILTERS * 361
 # DRAM traffic (read + write) of one conv_direct_kernel launch at 256 positions, from the committed ncu capture
-GEMM_DRAM_BYTES_PER_LAUNCH = 84.6e6   # mean of two captured launches (61 and 108 MB), profiles/conv_direct_kernel_40x256_batch256.md
+GEMM_DRAM_BYTES_PER_LAUNCH = 90.1e6   # mean of two captured launches (68 and 112 MB), profiles/conv_direct2_kernel_40x256_batch256.md
 
 
 def load_package():

@@ -38,12 +38,18 @@ def build(force=False, verbose=False):
         subprocess.run(cmd, check=True)
     if os.path.isdir(HOST):
         hsrcs = _sources(HOST, (".cpp", ".h"))
-        cpps = [s for s in hsrcs if s.endswith(".cpp")]
+        cpps = [s for s in hsrcs if s.endswith(".cpp") and not s.endswith("netbench.cpp")]
         if cpps and (force or not _newer(HOSTLIB, hsrcs + [LIB])):
             cmd = ["g++", "-std=c++14", "-O2", "-fPIC", "-shared", "-pthread",
                    "-I" + os.path.join(ROOT, "include"), "-I" + HOST, "-o", HOSTLIB] + cpps + [
                    "-L" + HERE, "-llzb200", "-Wl,-rpath,$ORIGIN"]
             subprocess.run(cmd, check=True)
+        nb = os.path.join(HOST, "netbench.cpp")
+        exe = os.path.join(HERE, "netbench")
+        if os.path.exists(nb) and (force or not _newer(exe, hsrcs + [LIB])):
+            subprocess.run(["g++", "-std=c++14", "-O2", "-pthread", "-I" + os.path.join(ROOT, "include"),
+                            "-I" + HOST, nb, os.path.join(HOST, "CUDAPipe.cpp"), "-L" + HERE, "-llzb200",
+                            "-Wl,-rpath,$ORIGIN", "-o", exe], check=True)
     return LIB
 
 
