@@ -310,7 +310,7 @@ def main():
                 "frac_of_sustained_peak": value * FLOPS_DIRECT / 1e12 / peaks["bf16_tflops_sustained"],
                 "per_gpu_tflops": value * FLOPS_DIRECT / 1e12 / world},
             "roofline": {"kernel": ("gemm_tc_kernel (36 Winograd channel contractions, tcgen05)" if winograd
-                                    else "conv_direct_kernel (3x3 conv + BN + residual + ReLU, implicit GEMM on tcgen05)"),
+                                    else "conv_direct2_kernel (3x3 conv + BN + residual + ReLU, implicit GEMM on tcgen05 CTA pairs)"),
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
                          "flops_per_launch": flops_per_launch, "avg_launch_ms": avg_s * 1e3,

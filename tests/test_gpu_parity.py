@@ -163,7 +163,7 @@ def test_config2_20x256_batch_sweep(lzb, oracle, W, n):
     128 positions is about 6e-3, which is the rounding floor of fp16 operands
     themselves (an exact-accumulation emulation of direct fp16 convolution
     gives 6.5e-3 over 96 positions), so the maximum is held to 1e-2.  bf16 has
-    8 fewer mantissa bits and is held to the engine's self-check only."""
+    3 fewer mantissa bits (8x coarser) and is held to the engine's self-check only."""
     net = W.synthetic_network(20, 256, 2003, calibrated=True)
     x = W.synthetic_positions(n, 1020)
     _, _, rp, rw = _reference(oracle, net, x)
