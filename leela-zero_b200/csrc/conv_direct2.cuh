@@ -91,13 +91,25 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
         : "memory");
 }
 
-// tmX : activations [Qa][Cin], box 64 x kWinRows.   tmW : weights [9*Kp][Cin], box 64 x Kp/2.
-// tmO : outputs [Qa][Kp], box 32 x 32, 64-byte swizzle.   npairs : 256-cell tiles covering Q.
+// tmX : activations [Qa][Cin], box 64 x kWinRows.
+// tmW : weights [9*Kp][Cin], box 64 x Kp/(2*nsplit).
+// tmO : outputs [Qa][Kp], box 32 x 32, 64-byte swizzle.
+// npairs : 256-cell tiles covering Q.  nsplit : the output channels of a tile are
+// cut into nsplit slices of N = Kp/nsplit (a multiple of 64), each slice a work
+// unit of its own; used when there are fewer tiles than CTA pairs, so that a
+// small batch spreads over more SMs.
+//
+// The kernel is launched with programmatic stream serialization: it lets its
+// successor start at once (griddepcontrol.launch_dependents) and itself waits
+// for its predecessor's results only after its own set-up (barriers, tensor
+// memory, batch-norm constants), which takes that set-up off the critical path
+// of a chain of small layers.
 template <typename T>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_direct2_kernel(
     const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
     const __grid_constant__ CUtensorMap tmO, const T* res, const float* __restrict__ bn_mean,
-    const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int npairs, int* err) {
+    const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int npairs, int nsplit,
+    int* err) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -118,6 +130,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * 40);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 40 + 8);
 
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
@@ -155,11 +168,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     cluster_sync_all();          // the peer's barriers are initialised before anyone signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Everything below reads what the previous kernel in the stream wrote.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    // work units: (tile, channel slice), numbered tile-major
     const int nclusters = gridDim.x >> 1, cid = blockIdx.x >> 1;
-    const int pair_begin = static_cast<int>(static_cast<long long>(cid) * npairs / nclusters);
-    const int pair_end = static_cast<int>(static_cast<long long>(cid + 1) * npairs / nclusters);
-    const int half_n = Kp >> 1;
+    const int units = npairs * nsplit;
+    const int unit_begin = static_cast<int>(static_cast<long long>(cid) * units / nclusters);
+    const int unit_end = static_cast<int>(static_cast<long long>(cid + 1) * units / nclusters);
+    const int n_slice = Kp / nsplit;          // MMA N
+    const int half_n = n_slice >> 1;          // weight rows each CTA stages
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer (both CTAs)
@@ -168,8 +186,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             uint32_t phase = 0, wphase = 0;
             bool ok = true;
             const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
-            for (int pair = pair_begin; pair < pair_end && ok; ++pair) {
+            for (int unit = unit_begin; unit < unit_end && ok; ++unit) {
+                const int pair = unit / nsplit, slice = unit - pair * nsplit;
                 const int m0 = pair * kPairM + static_cast<int>(rank) * kTileM;
+                const int wrow0 = slice * n_slice + static_cast<int>(rank) * half_n;
                 for (int c = 0; c < kchunks && ok; ++c) {
                     ok = mbar_wait(wempty_bar(wb), wphase ^ 1u, abort_flag, err, kErrD2Producer);
                     if (!ok) break;
@@ -183,7 +203,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                         const uint32_t bf = map_to_cta(bfull_bar(stage), 0);
                         mbar_expect_tx_cluster(bf, btx);
                         tma_load_2d_pair(b_base + stage * kB2StageBytes, &tmW, c * kChunkK,
-                                         tap * Kp + static_cast<int>(rank) * half_n, bf);
+                                         tap * Kp + wrow0, bf);
                         if (++stage == kB2Stages) { stage = 0; phase ^= 1u; }
                     }
                 }
@@ -194,13 +214,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
         if (lane == 0 && leader) {
             const uint32_t idesc = (1u << 4) | (OperandFormat<T>::value << 7) |
                                    (OperandFormat<T>::value << 10) |
-                                   (static_cast<uint32_t>(Kp >> 3) << 17) |
+                                   (static_cast<uint32_t>(n_slice >> 3) << 17) |
                                    (static_cast<uint32_t>(kPairM >> 4) << 24);
             int stage = 0, wb = 0;
             uint32_t phase = 0, wphase = 0;
             bool ok = true;
             int local = 0;
-            for (int pair = pair_begin; pair < pair_end && ok; ++pair, ++local) {
+            for (int unit = unit_begin; unit < unit_end && ok; ++unit, ++local) {
                 const int acc = local & 1;
                 const uint32_t accphase = (local >> 1) & 1u;
                 ok = mbar_wait(tempty_bar(acc), accphase ^ 1u, abort_flag, err, kErrD2MmaAcc);
@@ -237,13 +257,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     } else {
         // ------------------------------------------------ epilogue (warps 2..9, both CTAs)
         const int qd = warp & 3;
-        const int ncols = Kp >> 1;
-        const int col0 = ((warp - 2) >> 2) * ncols;
+        const int ncols = n_slice >> 1;          // channels this warp converts per unit
+        const int wcol = ((warp - 2) >> 2) * ncols;
         unsigned char* stg_ptr = stage_out + (warp - 2) * kStageOutBytes;
         const uint32_t stg = smem_u32(stg_ptr);
         unsigned char* stg_row = stg_ptr + lane * 64;
         int local = 0;
-        for (int pair = pair_begin; pair < pair_end; ++pair, ++local) {
+        for (int unit = unit_begin; unit < unit_end; ++unit, ++local) {
+            const int pair = unit / nsplit, slice = unit - pair * nsplit;
+            const int col0 = slice * n_slice + wcol;   // first output channel of this warp
             const int acc = local & 1;
             const uint32_t accphase = (local >> 1) & 1u;
             const int row0 = pair * kPairM + static_cast<int>(rank) * kTileM + qd * 32;
@@ -255,8 +277,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             tcgen05_fence_after();
             const bool use_res = (res != nullptr) && interior;
             const T* rrow = res + static_cast<size_t>(q) * Kp + col0;
+            // accumulator columns are numbered within the slice
             const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) +
-                                    static_cast<uint32_t>(acc * kMaxN + col0);
+                                    static_cast<uint32_t>(acc * kMaxN + wcol);
             uint32_t ra[32], rb[32];
             uint4 va[4], vb[4];
             load_residual(va, rrow, use_res);

@@ -107,7 +107,8 @@ struct Layer {
     CUtensorMap tmU;
     void* Wd = nullptr;         // direct path: [9][Kp][cin_p] storage type
     CUtensorMap tmW;            // box 64 x Kp   (one CTA per tile)
-    CUtensorMap tmW2;           // box 64 x Kp/2 (CTA pairs)
+    CUtensorMap tmW2[5];        // CTA pairs: [ns] has box 64 x Kp/(2*ns), ns = 1..4 where valid
+    bool split_ok[5] = {false, false, false, false, false};
 };
 
 struct Heads {
@@ -325,18 +326,40 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
     const int Q = static_cast<int>(dc::cells_for(nb));
     if (p->pairs) {
         const int npairs = (Q + dc2::kPairM - 1) / dc2::kPairM;
-        // Every CTA pair runs `rounds` tiles; use just enough pairs for that many
+        const int max_clusters = p->sm_count / 2;
+        // Small batches: cut the output channels of each tile into slices so that
+        // the layer spreads over more SMs (one slice per CTA pair).
+        int nsplit = 1;
+        for (int ns = 4; ns > 1; ns--) {
+            if (L.split_ok[ns] && npairs * ns <= max_clusters) {
+                nsplit = ns;
+                break;
+            }
+        }
+        // Every CTA pair runs `rounds` units; use just enough pairs for that many
         // rounds (400 tiles on 74 pairs need 6 rounds, which 67 pairs also do:
         // the idle SMs leave their power budget to the busy ones).
-        const int max_clusters = p->sm_count / 2;
-        const int rounds = (npairs + max_clusters - 1) / max_clusters;
-        const int clusters = (npairs + rounds - 1) / rounds;
+        const int units = npairs * nsplit;
+        const int rounds = (units + max_clusters - 1) / max_clusters;
+        const int clusters = (units + rounds - 1) / rounds;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * clusters);
+        cfg.blockDim = dim3(dc::kDcThreads);
+        cfg.dynamicSmemBytes = dc2::kD2SmemBytes;
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t le;
         {
             LaunchScope scope(c, kClassContraction);
-            dc2::conv_direct2_kernel<T><<<2 * clusters, dc::kDcThreads, dc2::kD2SmemBytes, c->stream>>>(
-                tm_in, L.tmW2, tm_out, res, L.mean, L.invstd, Q, p->Cp, L.cin_p / tc::kChunkK, npairs,
-                c->d_err);
+            le = cudaLaunchKernelEx(&cfg, dc2::conv_direct2_kernel<T>, tm_in, L.tmW2[nsplit], tm_out, res,
+                                    (const float*)L.mean, (const float*)L.invstd, Q, p->Cp,
+                                    L.cin_p / tc::kChunkK, npairs, nsplit, c->d_err);
         }
+        LZB_CUDA(le);
         LZB_CUDA(cudaGetLastError());
         return LZB_OK;
     }
@@ -640,7 +663,13 @@ int lzb_pipe_push_conv(lzb_pipe* p, int layer, const float* U, int c_in, const f
     if ((rc = upload_padded(&L.invstd, bn_invstd, p->channels, p->Cp))) return rc;
     if (p->direct) {
         rc = make_map_2d(&L.tmW, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p, p->Cp);
-        if (!rc) rc = make_map_2d(&L.tmW2, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p, p->Cp / 2);
+        for (int ns = 1; ns <= 4 && !rc; ns++) {
+            // a channel slice must be a multiple of 64 (two epilogue warps x 32 columns)
+            if (p->Cp % ns != 0 || (p->Cp / ns) % 64 != 0) continue;
+            rc = make_map_2d(&L.tmW2[ns], p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p,
+                             p->Cp / (2 * ns));
+            L.split_ok[ns] = (rc == LZB_OK);
+        }
         if (rc) return rc;
     } else if (p->precision != LZB_FP32) {
         rc = make_map_2d(&L.tmU, p->precision, L.U, (uint64_t)kPoints * p->Cp, L.cin_p, p->Cp);
