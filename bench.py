@@ -116,6 +116,22 @@ class ClockSampler:
         return out
 
 
+def max_over_ranks(ms, world, device=None):
+    """Slowest rank's time: the job is as fast as its slowest shard."""
+    if world <= 1:
+        return float(ms)
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device if device is not None else "cpu")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_rate(positions_per_rank, world, ms_slowest):
+    """positions/s of the whole job: every rank evaluates its own shard."""
+    return world * positions_per_rank / (ms_slowest * 1e-3)
+
+
 def cpu_reference_rate(net, weights_mod, positions, threads):
     """positions/s of the reference CPUPipe (or the C port) on host cores."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -256,10 +272,7 @@ def main():
         barrier()
         ms = sum(a.elapsed_time(b) for a, b in ev)
         launches = ctx.launches - launches0
-        if world > 1:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+        ms = max_over_ranks(ms, world, dev)
         return ms / steps, launches
 
     sampler = ClockSampler(local) if rank == 0 else None
@@ -277,8 +290,8 @@ def main():
 
     if rank == 0:
         peaks = measured_peaks()
-        value = world * B / (ms_dev * 1e-3)
-        e2e = world * B / (ms_e2e * 1e-3)
+        value = whole_job_rate(B, world, ms_dev)
+        e2e = whole_job_rate(B, world, ms_e2e)
         g_ms, g_n = prof["contraction"]
         winograd = args.precision != "fp16" and args.precision != "bf16"
         micro = args.micro_batch or (min(64, B) if winograd else B)

@@ -152,7 +152,7 @@ void CUDAPipe::forward(const std::vector<float>& input, std::vector<float>& outp
         m_queue.push_back(entry);
         // Requests arriving while a partial batch is in flight mean the wait
         // was too short (src/OpenCLScheduler.cpp:267-269).
-        if (m_partial_in_progress.load()) m_wait_ms += 2;
+        if (m_partial_in_progress.load() && m_wait_ms < kMaxWaitMs) m_wait_ms += 2;
     }
     m_cv.notify_one();
     std::unique_lock<std::mutex> lk(entry->mutex);

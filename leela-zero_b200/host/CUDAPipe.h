@@ -15,6 +15,8 @@
 //    src/OpenCLScheduler.cpp:272);
 //  * a GPU whose backend call fails is taken out of rotation, the callers of
 //    that batch get std::runtime_error, the other GPUs keep serving;
+//  * the adaptive wait for a full batch is capped at 100 ms (the reference lets it
+//    grow by 2 ms per arriving request without bound);
 //  * nothing here calls exit().
 #ifndef LZB_CUDAPIPE_H
 #define LZB_CUDAPIPE_H
@@ -85,6 +87,7 @@ public:
     static constexpr int kInputFloats = 18 * 361;
     static constexpr int kPolicyFloats = 2 * 361;
     static constexpr int kValueFloats = 361;
+    static constexpr int kMaxWaitMs = 100;
 
 private:
     struct Entry {
