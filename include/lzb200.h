@@ -188,6 +188,15 @@ int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n,
                        const float* residual, float* out);
 
 /*
+ * Diagnostics for tests: enqueue a kernel whose only wait can never be
+ * satisfied.  Like every device-side wait of this library it is bounded: after
+ * limit_ms (1..1000) it records an error code and returns, and the next
+ * lzb_ctx_sync reports LZB_ERR_DEVICE_WAIT.  The context stays usable.  No
+ * counterpart in the reference (its kernels have no inter-thread waits).
+ */
+int lzb_ctx_debug_wait_probe(lzb_ctx* c, int limit_ms);
+
+/*
  * One 3x3 layer (Winograd F(4x4,3x3) in fp32, then batch-norm, optional
  * residual, ReLU) that allocates nothing.  This entry point has no counterpart
  * in the reference.

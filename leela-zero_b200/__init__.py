@@ -28,7 +28,7 @@ SYMBOLS = (
     "lzb_ctx_forward_device", "lzb_ctx_forward_heads", "lzb_ctx_forward_heads_device",
     "lzb_ctx_sync", "lzb_ctx_stream", "lzb_ctx_set_micro_batch", "lzb_ctx_launch_count",
     "lzb_ctx_debug_conv", "lzb_ctx_profile_begin", "lzb_ctx_profile_end",
-    "lzb_conv3x3_static",
+    "lzb_conv3x3_static", "lzb_ctx_debug_wait_probe",
 )
 
 _f32p = ctypes.POINTER(ctypes.c_float)
@@ -71,6 +71,7 @@ def lib():
         L.lzb_ctx_debug_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
         L.lzb_ctx_profile_begin.argtypes = [vp]
         L.lzb_ctx_profile_end.argtypes = [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]
+        L.lzb_ctx_debug_wait_probe.argtypes = [vp, ctypes.c_int]
         L.lzb_conv3x3_static.argtypes = [ctypes.c_int, vp, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                          vp, vp, vp, vp, vp, vp]
         _lib = L
@@ -206,6 +207,10 @@ class Context:
         check(lib().lzb_ctx_profile_end(self.h, ms, cnt))
         names = ("contraction", "transform", "input", "head")
         return {k: (ms[i], cnt[i]) for i, k in enumerate(names)}
+
+    def debug_wait_probe(self, limit_ms=50):
+        """Enqueue a bounded wait that runs out (see lzb_ctx_debug_wait_probe)."""
+        check(lib().lzb_ctx_debug_wait_probe(self.h, limit_ms))
 
     def debug_conv(self, layer, x, residual=None):
         """One 3x3 layer on fp32 NCHW host data (diagnostics)."""

@@ -168,9 +168,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     cluster_sync_all();          // the peer's barriers are initialised before anyone signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // Everything below reads what the previous kernel in the stream wrote.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-
     // work units: (tile, channel slice), numbered tile-major
     const int nclusters = gridDim.x >> 1, cid = blockIdx.x >> 1;
     const int units = npairs * nsplit;
@@ -178,6 +175,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     const int unit_end = static_cast<int>(static_cast<long long>(cid + 1) * units / nclusters);
     const int n_slice = Kp / nsplit;          // MMA N
     const int half_n = n_slice >> 1;          // weight rows each CTA stages
+
+    // Activations, residuals and outputs belong to the chain of kernels in the
+    // stream: nobody touches them before the previous kernel has finished.
+    // (Starting the constant weight tiles ahead of this wait was tried and made
+    // no measurable difference.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer (both CTAs)
@@ -271,8 +274,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             const int row0 = pair * kPairM + static_cast<int>(rank) * kTileM + qd * 32;
             const int q = row0 + lane;
             const bool interior = cell_is_interior(q, Q);
-            bool ok = mbar_wait(tfull_bar(acc), accphase, abort_flag, err, kErrD2Epilogue);
-            ok = __all_sync(0xffffffffu, ok);
+            // one lane polls, the others sleep at the warp barrier
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait(tfull_bar(acc), accphase, abort_flag, err, kErrD2Epilogue);
+            ok = __shfl_sync(0xffffffffu, ok, 0);
             if (!ok) break;
             tcgen05_fence_after();
             const bool use_res = (res != nullptr) && interior;

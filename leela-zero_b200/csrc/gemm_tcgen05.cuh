@@ -88,13 +88,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false if the CTA is aborting or the limit ran out.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            int* err, int code) {
+                                            int* err, int code,
+                                            unsigned long long limit_ns = kWaitLimitNs) {
     const unsigned long long t0 = globaltimer_ns();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 31u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(err, 0, code);
                 return false;

@@ -231,8 +231,8 @@ struct LaunchScope {
     }
 };
 
-template <typename T>
-int launch_gemm(lzb_ctx* c, const Layer& L, int P) {
+// fp32: FFMA contraction.
+int launch_gemm_f32(lzb_ctx* c, const Layer& L, int P) {
     lzb_pipe* p = c->pipe;
     {
         LaunchScope scope(c, kClassContraction);
@@ -245,6 +245,7 @@ int launch_gemm(lzb_ctx* c, const Layer& L, int P) {
     return LZB_OK;
 }
 
+// 16-bit: tcgen05 contraction, persistent CTAs.
 template <typename T>
 int launch_gemm_tc(lzb_ctx* c, const Layer& L, int P, bool first) {
     lzb_pipe* p = c->pipe;
@@ -261,14 +262,14 @@ int launch_gemm_tc(lzb_ctx* c, const Layer& L, int P, bool first) {
     return LZB_OK;
 }
 
+// The 36 channel contractions of one layer in the storage type T.
 template <typename T>
 int contraction(lzb_ctx* c, const Layer& L, int P, bool first) {
-    if (c->pipe->precision == LZB_FP32) return launch_gemm<float>(c, L, P);
     return launch_gemm_tc<T>(c, L, P, first);
 }
 template <>
 int contraction<float>(lzb_ctx* c, const Layer& L, int P, bool) {
-    return launch_gemm<float>(c, L, P);
+    return launch_gemm_f32(c, L, P);
 }
 
 template <typename T>
@@ -548,6 +549,29 @@ int debug_conv_t(lzb_ctx* c, int layer, const float* in, int n, const float* res
     int rc2 = lzb_ctx_sync(c);
     cudaFree(stage);
     return rc ? rc : rc2;
+}
+}  // namespace
+
+// A wait that nothing will ever satisfy, bounded like every wait in the
+// tensor-core kernels: the barrier expects one arrival and nobody arrives, so
+// the wait runs out after limit_ns, records its code and the kernel returns
+// normally.  Used to check, without hanging anything, that a kernel giving up
+// a wait reaches the host as LZB_ERR_DEVICE_WAIT and leaves the context usable.
+namespace {
+constexpr int kErrWaitProbe = 900;
+__global__ void wait_probe_kernel(int* err, unsigned long long limit_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    const uint32_t b = lzb::tc::smem_u32(&bar);
+    if (threadIdx.x == 0) {
+        lzb::tc::mbar_init(b, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !lzb::tc::mbar_try_wait(b, 0)) {
+        lzb::tc::mbar_wait_slow(b, 0, &abort_flag, err, kErrWaitProbe, limit_ns);
+    }
 }
 }  // namespace
 
@@ -1026,6 +1050,16 @@ int lzb_conv3x3_static(int device, const float* in_dev, int n, int c_in, int cha
     xform_kernel<float><<<tgrid, kXformThreads, tsmem, stream>>>(M, kStaticRows, Cp, bn, bn + 64, R, X,
                                                                   nullptr);
     nhwc_to_nchw_kernel<float><<<128, 256, 0, stream>>>(X, out_dev, n, channels, Cp);
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+
+int lzb_ctx_debug_wait_probe(lzb_ctx* c, int limit_ms) {
+    if (!c) return fail(LZB_ERR_ARG, "null context");
+    if (limit_ms < 1 || limit_ms > 1000) return fail(LZB_ERR_ARG, "limit must be 1..1000 ms");
+    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    wait_probe_kernel<<<1, 32, 0, c->stream>>>(c->d_err, (unsigned long long)limit_ms * 1000000ull);
+    c->launches++;
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }

@@ -317,6 +317,28 @@ def test_single_cta_and_cta_pair_kernels_agree(lzb, W, monkeypatch):
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
 
 
+def test_device_wait_that_runs_out_is_reported_and_survivable(lzb, W):
+    """Failure detection without a fault: a kernel whose barrier nobody signals
+    gives up after its limit, the host sees LZB_ERR_DEVICE_WAIT (code 3) with
+    the kernel's own code in the text, and the same context then evaluates
+    positions correctly."""
+    import time
+    net = W.synthetic_network(2, 64, 2058, calibrated=True)
+    x = W.synthetic_positions(4, 1058)
+    ctx = lzb.Pipe(net, "fp16").context(4)
+    want = ctx.forward(x)
+    t0 = time.perf_counter()
+    ctx.debug_wait_probe(limit_ms=50)
+    with pytest.raises(lzb.LzbError) as e:
+        ctx.sync()
+    waited = time.perf_counter() - t0
+    assert e.value.code == 3 and "900" in str(e.value)
+    assert 0.04 <= waited < 1.0                   # it waited for its limit, not forever
+    ctx.sync()                                     # the flag is cleared once reported
+    got = ctx.forward(x)
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
+
+
 def test_profile_counters(lzb, W):
     net = W.synthetic_network(2, 64, 2056)
     ctx = lzb.Pipe(net, "fp16").context(4)
