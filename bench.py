@@ -32,6 +32,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 
 BLOCKS, FILTERS, BATCH = 40, 256, 256
 WEIGHT_SEED, INPUT_SEED = 2003, 1003
+WORKLOAD = ("config 3: 40 blocks x 256 filters, %d positions per GPU per step, "
+            "tower + 1x1 head convs + policy/value heads")
 PRECISION = "fp16"
 # direct-convolution FLOPs per position, tower + 1x1 convs + the three FC layers
 FLOPS_DIRECT = (2 * 9 * 18 * FILTERS * 361 + 2 * BLOCKS * 2 * 9 * FILTERS * FILTERS * 361
@@ -181,8 +183,9 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "40b x 256f tower + heads, CPUPipe on host cores",
-                   "blocks": BLOCKS, "filters": FILTERS},
+        "config": {"workload": WORKLOAD % BATCH, "blocks": BLOCKS, "filters": FILTERS,
+                   "batch_per_gpu": BATCH,
+                   "note": "the reference's CPUPipe on the host cores, bounded sample of the workload"},
         "cpu_baseline": {"value": value, "unit": "positions/s", "cores": threads, "kind": kind,
                          "sample": sample},
         "e2e": {"value": value, "unit": "positions/s", "h2d_bytes_per_step": 0,
@@ -306,8 +309,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": args.precision + " operands, f32 accumulate", "data": "synthetic",
-            "config": {"workload": "config 3: 40 blocks x 256 filters, %d positions per GPU per step, "
-                                   "tower + 1x1 head convs + policy/value heads on device" % B,
+            "config": {"workload": WORKLOAD % B,
                        "blocks": BLOCKS, "filters": FILTERS, "batch_per_gpu": B,
                        "micro_batch": micro, "parallelism": "replicas, positions sharded, no collective",
                        "l2": "256 MB buffer written between timed steps (L2 flush); weights 378 MB > L2"},

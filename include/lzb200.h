@@ -150,6 +150,15 @@ int lzb_ctx_forward_heads_device(lzb_ctx* c, const float* in_dev, int n,
                                  float softmax_temp, float* policy_dev,
                                  float* winrate_dev);
 
+/*
+ * Page-locked host memory for batch staging.  Host buffers handed to
+ * lzb_ctx_forward may be any memory, but copies from and to page-locked memory
+ * run at full PCIe speed and asynchronously.  Replaces the pinned output
+ * buffers of the reference (CL_MEM_ALLOC_HOST_PTR, src/OpenCL.cpp:192-199).
+ */
+int lzb_host_alloc(void** out, size_t bytes);
+void lzb_host_free(void* p);
+
 /* Wait for everything enqueued on the context; reports device-side errors. */
 int lzb_ctx_sync(lzb_ctx* c);
 

@@ -28,7 +28,7 @@ SYMBOLS = (
     "lzb_ctx_forward_device", "lzb_ctx_forward_heads", "lzb_ctx_forward_heads_device",
     "lzb_ctx_sync", "lzb_ctx_stream", "lzb_ctx_set_micro_batch", "lzb_ctx_launch_count",
     "lzb_ctx_debug_conv", "lzb_ctx_profile_begin", "lzb_ctx_profile_end",
-    "lzb_conv3x3_static", "lzb_ctx_debug_wait_probe",
+    "lzb_conv3x3_static", "lzb_ctx_debug_wait_probe", "lzb_host_alloc", "lzb_host_free",
 )
 
 _f32p = ctypes.POINTER(ctypes.c_float)
@@ -71,6 +71,9 @@ def lib():
         L.lzb_ctx_debug_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
         L.lzb_ctx_profile_begin.argtypes = [vp]
         L.lzb_ctx_profile_end.argtypes = [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]
+        L.lzb_host_alloc.argtypes = [ctypes.POINTER(vp), ctypes.c_size_t]
+        L.lzb_host_free.argtypes = [vp]
+        L.lzb_host_free.restype = None
         L.lzb_ctx_debug_wait_probe.argtypes = [vp, ctypes.c_int]
         L.lzb_conv3x3_static.argtypes = [ctypes.c_int, vp, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                          vp, vp, vp, vp, vp, vp]

@@ -590,6 +590,21 @@ int lzb_device_count(int* count) {
     return LZB_OK;
 }
 
+int lzb_host_alloc(void** out, size_t bytes) {
+    if (!out || bytes == 0) return fail(LZB_ERR_ARG, "bad host allocation request");
+    *out = nullptr;
+    cudaError_t e = cudaMallocHost(out, bytes);
+    if (e != cudaSuccess) {
+        return fail(e == cudaErrorMemoryAllocation ? LZB_ERR_NOMEM : LZB_ERR_CUDA,
+                    std::string("cudaMallocHost: ") + cudaGetErrorString(e));
+    }
+    return LZB_OK;
+}
+
+void lzb_host_free(void* p) {
+    if (p) cudaFreeHost(p);
+}
+
 int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int precision) {
     if (!out) return fail(LZB_ERR_ARG, "null out");
     *out = nullptr;

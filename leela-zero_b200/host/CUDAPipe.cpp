@@ -51,6 +51,13 @@ public:
         return rc;
     }
 
+    float* alloc_staging(std::size_t floats) override {
+        void* p = nullptr;
+        check(lzb_host_alloc(&p, floats * sizeof(float)));
+        return static_cast<float*>(p);
+    }
+    void free_staging(float* p) override { lzb_host_free(p); }
+
 private:
     static void check(int rc) {
         // Initialisation failures surface as std::runtime_error, as in the
@@ -193,9 +200,18 @@ std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out) {
 }
 
 void CUDAPipe::worker(int gpu_index, int slot) {
-    std::vector<float> in(static_cast<size_t>(m_batch_size) * kInputFloats);
-    std::vector<float> pol(static_cast<size_t>(m_batch_size) * kPolicyFloats);
-    std::vector<float> val(static_cast<size_t>(m_batch_size) * kValueFloats);
+    // Staging buffers of this worker, released when it leaves.
+    struct Staging {
+        Backend* b;
+        float* p;
+        Staging(Backend* backend, size_t n) : b(backend), p(backend->alloc_staging(n)) {}
+        ~Staging() { b->free_staging(p); }
+        float* data() { return p; }
+        float& operator[](size_t i) { return p[i]; }
+    };
+    Staging in(m_backend.get(), static_cast<size_t>(m_batch_size) * kInputFloats);
+    Staging pol(m_backend.get(), static_cast<size_t>(m_batch_size) * kPolicyFloats);
+    Staging val(m_backend.get(), static_cast<size_t>(m_batch_size) * kValueFloats);
     while (true) {
         {
             std::lock_guard<std::mutex> lk(m_mutex);

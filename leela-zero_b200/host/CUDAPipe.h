@@ -55,6 +55,10 @@ public:
         // pol [n][2*361], val [n][361].  Returns 0 or an error code and text.
         virtual int forward(int gpu_index, int worker, const float* in, int n, float* pol,
                             float* val, std::string* error) = 0;
+        // Staging memory for a worker's batches (page-locked in the production
+        // backend); the default is ordinary memory.
+        virtual float* alloc_staging(std::size_t floats) { return new float[floats]; }
+        virtual void free_staging(float* p) { delete[] p; }
     };
 
     struct Stats {
