@@ -159,7 +159,7 @@ def run_reference(args):
         return
     pkg_w = load_package().weights
     cores = os.cpu_count() or 1
-    net = pkg_w.synthetic_network(BLOCKS, FILTERS, WEIGHT_SEED)
+    net = pkg_w.synthetic_network(BLOCKS, FILTERS, WEIGHT_SEED, calibrated=True)
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import oracle as O
     kind = "reference" if O.ref_available() else "port"
@@ -223,7 +223,7 @@ def main():
 
     pkg = load_package()
     W = pkg.weights
-    net = W.synthetic_network(BLOCKS, FILTERS, WEIGHT_SEED)
+    net = W.synthetic_network(BLOCKS, FILTERS, WEIGHT_SEED, calibrated=True)
     pipe = pkg.Pipe(net, args.precision, device=local)
     B = args.batch
     ctx = pipe.context(B)
@@ -291,6 +291,11 @@ def main():
         step_device(i)
     prof = ctx.profile_end()
 
+    # the last step's results must be a valid evaluation (finite, policies sum to 1)
+    pol_ok = bool(torch.isfinite(policy_host).all() and torch.isfinite(win_host).all()
+                  and (policy_host.sum(1) - 1).abs().max() < 1e-3
+                  and ((win_host >= 0) & (win_host <= 1)).all())
+
     if rank == 0:
         peaks = measured_peaks()
         value = whole_job_rate(B, world, ms_dev)
@@ -316,6 +321,7 @@ def main():
             "e2e": {"value": e2e, "unit": "positions/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": B * 18 * 361 * 4, "d2h_bytes_per_step": B * 363 * 4},
             "gpu_launches": launches,
+            "outputs_valid": pol_ok,
             "clocks": clocks,
             "tensor_credit": {
                 "note": "direct-convolution FLOPs per position x positions/s over measured bf16 peak",

@@ -37,6 +37,9 @@ extern "C" {
  *  LZB_FP16, LZB_BF16  16-bit operands on the tensor cores (tcgen05), fp32
  *                      accumulation; each 3x3 layer is one implicit-GEMM
  *                      convolution with batch-norm/residual/ReLU in its epilogue.
+ *                      (Runs on CTA pairs; the environment variable
+ *                      LZB_CONV_PAIRS=0, read at lzb_pipe_create, selects the
+ *                      bit-identical single-CTA kernel for diagnostics.)
  *  LZB_*_WINOGRAD      16-bit operands on the tensor cores through the Winograd
  *                      pipeline (transform, 36 batched contractions, fused
  *                      output/input transform).  3.6x fewer multiply-adds, about
@@ -88,6 +91,17 @@ void lzb_pipe_destroy(lzb_pipe* p);
  */
 int lzb_pipe_push_conv(lzb_pipe* p, int layer, const float* U, int c_in,
                        const float* bn_mean, const float* bn_invstd);
+
+/*
+ * Same as lzb_pipe_push_conv, but from the UNTRANSFORMED filters as they stand
+ * in a weights file: f fp32 [channels][c_in][3][3].  The Winograd modes compute
+ * U = G f G^T on the GPU (the arithmetic of Network::winograd_transform_f,
+ * src/Network.cpp:159-223); the direct-convolution modes use f as it is, which
+ * spares them the recovery of f from U.  For hosts that own the weights file
+ * rather than the engine's already transformed ForwardPipeWeights.
+ */
+int lzb_pipe_push_conv_filters(lzb_pipe* p, int layer, const float* f, int c_in,
+                               const float* bn_mean, const float* bn_invstd);
 
 /*
  * Upload the two 1x1 head convolutions: pol_w fp32 [2][channels], val_w fp32
@@ -149,6 +163,20 @@ int lzb_ctx_forward_heads(lzb_ctx* c, const float* in, int n, float softmax_temp
 int lzb_ctx_forward_heads_device(lzb_ctx* c, const float* in_dev, int n,
                                  float softmax_temp, float* policy_dev,
                                  float* winrate_dev);
+
+/*
+ * Bit-packed positions.  The 18 input planes hold only zeros and ones
+ * (src/Network.cpp:935-966), so a position can travel as 18 x 12 32-bit words
+ * (bit i of word w of a plane = board cell 32 w + i; 864 bytes instead of the
+ * 25,992 the fp32 planes take: 30x less host-to-device traffic).  planes is
+ * HOST memory [n][18][12]; outputs as lzb_ctx_forward / lzb_ctx_forward_heads.
+ * The planes are expanded on the GPU and then take the normal path, so results
+ * are identical to the fp32 entry points.
+ */
+#define LZB_PACKED_WORDS (18 * 12)
+int lzb_ctx_forward_packed(lzb_ctx* c, const unsigned int* planes, int n, float* pol, float* val);
+int lzb_ctx_forward_heads_packed(lzb_ctx* c, const unsigned int* planes, int n, float softmax_temp,
+                                 float* policy, float* winrate);
 
 /*
  * Page-locked host memory for batch staging.  Host buffers handed to

@@ -29,6 +29,7 @@ SYMBOLS = (
     "lzb_ctx_sync", "lzb_ctx_stream", "lzb_ctx_set_micro_batch", "lzb_ctx_launch_count",
     "lzb_ctx_debug_conv", "lzb_ctx_profile_begin", "lzb_ctx_profile_end",
     "lzb_conv3x3_static", "lzb_ctx_debug_wait_probe", "lzb_host_alloc", "lzb_host_free",
+    "lzb_pipe_push_conv_filters", "lzb_ctx_forward_packed", "lzb_ctx_forward_heads_packed",
 )
 
 _f32p = ctypes.POINTER(ctypes.c_float)
@@ -71,6 +72,9 @@ def lib():
         L.lzb_ctx_debug_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
         L.lzb_ctx_profile_begin.argtypes = [vp]
         L.lzb_ctx_profile_end.argtypes = [vp, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]
+        L.lzb_pipe_push_conv_filters.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
+        L.lzb_ctx_forward_packed.argtypes = [vp, vp, ctypes.c_int, vp, vp]
+        L.lzb_ctx_forward_heads_packed.argtypes = [vp, vp, ctypes.c_int, ctypes.c_float, vp, vp]
         L.lzb_host_alloc.argtypes = [ctypes.POINTER(vp), ctypes.c_size_t]
         L.lzb_host_free.argtypes = [vp]
         L.lzb_host_free.restype = None
@@ -91,6 +95,16 @@ def _ptr(a):
     return a.ctypes.data_as(_f32p)
 
 
+def pack_positions(x):
+    """0/1 planes ``[n][18][19][19]`` -> ``[n][18][12]`` uint32, bit i of word w of a
+    plane = board cell 32 w + i (the layout lzb_ctx_forward_packed takes)."""
+    x = np.asarray(x).reshape(-1, 18, 361)
+    bits = np.zeros((x.shape[0], 18, 384), np.uint8)
+    bits[:, :, :361] = x != 0
+    words = np.packbits(bits.reshape(-1, 18, 12, 32), axis=-1, bitorder="little")
+    return np.ascontiguousarray(words).view(np.uint32).reshape(-1, 18, 12)
+
+
 def device_count():
     n = ctypes.c_int(0)
     check(lib().lzb_device_count(ctypes.byref(n)))
@@ -106,7 +120,7 @@ class Pipe:
     ``pol_w`` ``[2][C]``, ``val_w`` ``[1][C]``, plus optionally ``heads``.
     """
 
-    def __init__(self, net, precision="fp16", device=0, heads=True):
+    def __init__(self, net, precision="fp16", device=0, heads=True, from_filters=False):
         L = lib()
         self.h = ctypes.c_void_p()
         self.channels, self.blocks = net["channels"], net["blocks"]
@@ -114,10 +128,14 @@ class Pipe:
         check(L.lzb_pipe_create(ctypes.byref(self.h), device, self.channels, self.blocks,
                                 self.precision))
         for l, U in enumerate(net["U"]):
-            U = np.ascontiguousarray(U, np.float32)
-            check(L.lzb_pipe_push_conv(self.h, l, _ptr(U), U.shape[1],
-                                       _ptr(np.ascontiguousarray(net["bn_mean"][l], np.float32)),
-                                       _ptr(np.ascontiguousarray(net["bn_invstd"][l], np.float32))))
+            mean = _ptr(np.ascontiguousarray(net["bn_mean"][l], np.float32))
+            inv = _ptr(np.ascontiguousarray(net["bn_invstd"][l], np.float32))
+            if from_filters:      # untransformed filters [K][c_in][3][3], as in a weights file
+                f = np.ascontiguousarray(net["filters"][l], np.float32)
+                check(L.lzb_pipe_push_conv_filters(self.h, l, _ptr(f), f.shape[1], mean, inv))
+            else:                 # Winograd-transformed, as the engine hands them to a pipe
+                U = np.ascontiguousarray(U, np.float32)
+                check(L.lzb_pipe_push_conv(self.h, l, _ptr(U), U.shape[1], mean, inv))
         check(L.lzb_pipe_push_head_convs(self.h, _ptr(np.ascontiguousarray(net["pol_w"], np.float32)),
                                          _ptr(np.ascontiguousarray(net["val_w"], np.float32))))
         self.has_heads = bool(heads and "heads" in net)
@@ -170,6 +188,25 @@ class Context:
         win = np.empty(n, np.float32)
         check(lib().lzb_ctx_forward_heads(self.h, x.ctypes.data, n, softmax_temp,
                                           policy.ctypes.data, win.ctypes.data))
+        return policy, win
+
+    def forward_packed(self, packed):
+        """Bit-packed positions ``[n][18][12]`` uint32 (see :func:`pack_positions`)."""
+        packed = np.ascontiguousarray(packed, np.uint32).reshape(-1, 18 * 12)
+        n = packed.shape[0]
+        pol = np.empty((n, POL_FLOATS), np.float32)
+        val = np.empty((n, VAL_FLOATS), np.float32)
+        check(lib().lzb_ctx_forward_packed(self.h, packed.ctypes.data, n, pol.ctypes.data,
+                                           val.ctypes.data))
+        return pol, val
+
+    def forward_heads_packed(self, packed, softmax_temp=1.0):
+        packed = np.ascontiguousarray(packed, np.uint32).reshape(-1, 18 * 12)
+        n = packed.shape[0]
+        policy = np.empty((n, MOVES), np.float32)
+        win = np.empty(n, np.float32)
+        check(lib().lzb_ctx_forward_heads_packed(self.h, packed.ctypes.data, n, softmax_temp,
+                                                 policy.ctypes.data, win.ctypes.data))
         return policy, win
 
     def forward_ptr(self, in_ptr, n, pol_ptr, val_ptr):

@@ -425,6 +425,17 @@ __global__ void untransform_u_kernel(const float* __restrict__ U32, T* __restric
     }
 }
 
+// Untransformed filters f[K][c_in][3][3] -> Wd[9][Kp][Cin_p] (Wd zeroed beforehand).
+template <typename T>
+__global__ void filters_to_wd_kernel(const float* __restrict__ f, T* __restrict__ Wd, int c_in, int K,
+                                     int Cin_p, int Kp) {
+    const int total = c_in * K * 9;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int tap = i % 9, c = (i / 9) % c_in, k = i / (9 * c_in);
+        Wd[((size_t)tap * Kp + k) * Cin_p + c] = (T)f[i];
+    }
+}
+
 // 1x1 head convolutions reading the padded cell-major layout (see
 // head_conv_kernel for the arithmetic).  One warp per board cell.
 template <typename T>

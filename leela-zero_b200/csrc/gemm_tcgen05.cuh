@@ -87,15 +87,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false if the CTA is aborting or the limit ran out.
+// The limit must be exceeded on two independent counters, the global
+// nanosecond timer and the SM cycle counter (>= 1 cycle per ns at any clock the
+// part runs kernels at), so that a step in either of them cannot end a wait
+// early.
 __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                             int* err, int code,
                                             unsigned long long limit_ns = kWaitLimitNs) {
     const unsigned long long t0 = globaltimer_ns();
+    const long long c0 = clock64();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 31u) == 0u) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > limit_ns) {
+            if (globaltimer_ns() - t0 > limit_ns &&
+                static_cast<unsigned long long>(clock64() - c0) > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(err, 0, code);
                 return false;

@@ -147,6 +147,7 @@ struct lzb_ctx {
     void *V = nullptr, *M = nullptr, *X = nullptr;
     float *d_in = nullptr, *d_pol = nullptr, *d_val = nullptr;
     float *d_policy = nullptr, *d_winrate = nullptr;
+    unsigned int* d_packed = nullptr;   // bit-packed input planes [max_batch][18][12]
     int* d_err = nullptr;
     int* h_err = nullptr;  // pinned
     CUtensorMap tmV_first, tmV;
@@ -575,6 +576,98 @@ __global__ void wait_probe_kernel(int* err, unsigned long long limit_ns) {
 }
 }  // namespace
 
+namespace {
+// Upload one 3x3 layer from either the Winograd-transformed U[36][c_in][K] or
+// the plain filters f[K][c_in][3][3] and bring it into the layout of the
+// pipe's mode.
+int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float* bn_mean,
+                 const float* bn_invstd, bool src_is_filters) {
+    if (!p || !src || !bn_mean || !bn_invstd) return fail(LZB_ERR_ARG, "null argument");
+    if (p->finalized) return fail(LZB_ERR_ARG, "pipe already finalized");
+    if (layer < 0 || layer >= (int)p->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
+    const int want = layer == 0 ? kInputPlanes : p->channels;
+    if (c_in != want) return fail(LZB_ERR_ARG, "c_in does not match the layer");
+    LZB_CUDA(cudaSetDevice(p->device));
+    Layer& L = p->layers[layer];
+    if (L.present) return fail(LZB_ERR_ARG, "layer pushed twice");
+    L.cin_p = round_up(c_in, 64);
+    const int K = p->channels;
+    const size_t n_src = (size_t)(src_is_filters ? 9 : kPoints) * c_in * K;
+    const size_t n_u32 = (size_t)kPoints * c_in * K;
+    float* src_dev = nullptr;
+    float* U32 = nullptr;            // transformed filters on the device (Winograd modes)
+    LZB_CUDA(cudaMalloc(&src_dev, n_src * sizeof(float)));
+    cudaError_t e = cudaMemcpy(src_dev, src, n_src * sizeof(float), cudaMemcpyHostToDevice);
+    int rc = LZB_OK;
+    if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("weight upload: ") + cudaGetErrorString(e));
+    if (rc == LZB_OK && p->direct && src_is_filters) {
+        // plain filters into the implicit-GEMM layout, no transform involved
+        const size_t n = (size_t)9 * p->Cp * L.cin_p * p->elt;
+        e = cudaMalloc(&L.Wd, n);
+        if (e == cudaSuccess) e = cudaMemset(L.Wd, 0, n);
+        if (e == cudaSuccess) {
+            if (p->precision == LZB_FP16) {
+                dc::filters_to_wd_kernel<__half><<<256, 256>>>(src_dev, static_cast<__half*>(L.Wd), c_in, K,
+                                                               L.cin_p, p->Cp);
+            } else {
+                dc::filters_to_wd_kernel<__nv_bfloat16><<<256, 256>>>(
+                    src_dev, static_cast<__nv_bfloat16*>(L.Wd), c_in, K, L.cin_p, p->Cp);
+            }
+            e = cudaGetLastError();
+        }
+        if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("filter upload: ") + cudaGetErrorString(e));
+    } else if (rc == LZB_OK) {
+        const float* u_dev = src_dev;
+        if (src_is_filters) {
+            e = cudaMalloc(&U32, n_u32 * sizeof(float));
+            if (e == cudaSuccess) {
+                transform_f_kernel<<<256, 256>>>(src_dev, U32, c_in, K);
+                e = cudaGetLastError();
+            }
+            if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("filter transform: ") + cudaGetErrorString(e));
+            u_dev = U32;
+        }
+        if (rc == LZB_OK) {
+            if (p->direct) {
+                rc = p->precision == LZB_FP16 ? upload_layer_direct_t<__half>(p, L, u_dev, c_in)
+                                              : upload_layer_direct_t<__nv_bfloat16>(p, L, u_dev, c_in);
+            } else if (p->precision == LZB_FP32) {
+                rc = upload_layer_t<float>(p, L, u_dev, c_in);
+            } else if (p->precision == LZB_FP16) {
+                rc = upload_layer_t<__half>(p, L, u_dev, c_in);
+            } else {
+                rc = upload_layer_t<__nv_bfloat16>(p, L, u_dev, c_in);
+            }
+        }
+    }
+    if (rc == LZB_OK) {
+        e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("weight repack: ") + cudaGetErrorString(e));
+    }
+    cudaFree(src_dev);
+    cudaFree(U32);
+    if (rc) return rc;
+    if ((rc = upload_padded(&L.mean, bn_mean, p->channels, p->Cp))) return rc;
+    if ((rc = upload_padded(&L.invstd, bn_invstd, p->channels, p->Cp))) return rc;
+    if (p->direct) {
+        rc = make_map_2d(&L.tmW, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p, p->Cp);
+        for (int ns = 1; ns <= 4 && !rc; ns++) {
+            // a channel slice must be a multiple of 64 (two epilogue warps x 32 columns)
+            if (p->Cp % ns != 0 || (p->Cp / ns) % 64 != 0) continue;
+            rc = make_map_2d(&L.tmW2[ns], p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p,
+                             p->Cp / (2 * ns));
+            L.split_ok[ns] = (rc == LZB_OK);
+        }
+        if (rc) return rc;
+    } else if (p->precision != LZB_FP32) {
+        rc = make_map_2d(&L.tmU, p->precision, L.U, (uint64_t)kPoints * p->Cp, L.cin_p, p->Cp);
+        if (rc) return rc;
+    }
+    L.present = true;
+    return LZB_OK;
+}
+}  // namespace
+
 // ===========================================================================
 // C ABI
 // ===========================================================================
@@ -666,56 +759,12 @@ void lzb_pipe_destroy(lzb_pipe* p) {
 
 int lzb_pipe_push_conv(lzb_pipe* p, int layer, const float* U, int c_in, const float* bn_mean,
                        const float* bn_invstd) {
-    if (!p || !U || !bn_mean || !bn_invstd) return fail(LZB_ERR_ARG, "null argument");
-    if (p->finalized) return fail(LZB_ERR_ARG, "pipe already finalized");
-    if (layer < 0 || layer >= (int)p->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
-    const int want = layer == 0 ? kInputPlanes : p->channels;
-    if (c_in != want) return fail(LZB_ERR_ARG, "c_in does not match the layer");
-    LZB_CUDA(cudaSetDevice(p->device));
-    Layer& L = p->layers[layer];
-    if (L.present) return fail(LZB_ERR_ARG, "layer pushed twice");
-    L.cin_p = round_up(c_in, 64);
-    float* U32 = nullptr;
-    const size_t n32 = (size_t)kPoints * c_in * p->channels;
-    LZB_CUDA(cudaMalloc(&U32, n32 * sizeof(float)));
-    cudaError_t e = cudaMemcpy(U32, U, n32 * sizeof(float), cudaMemcpyHostToDevice);
-    int rc = LZB_OK;
-    if (e != cudaSuccess) {
-        rc = fail(LZB_ERR_CUDA, std::string("weight upload: ") + cudaGetErrorString(e));
-    } else if (p->direct) {
-        rc = p->precision == LZB_FP16 ? upload_layer_direct_t<__half>(p, L, U32, c_in)
-                                      : upload_layer_direct_t<__nv_bfloat16>(p, L, U32, c_in);
-    } else if (p->precision == LZB_FP32) {
-        rc = upload_layer_t<float>(p, L, U32, c_in);
-    } else if (p->precision == LZB_FP16) {
-        rc = upload_layer_t<__half>(p, L, U32, c_in);
-    } else {
-        rc = upload_layer_t<__nv_bfloat16>(p, L, U32, c_in);
-    }
-    if (rc == LZB_OK) {
-        e = cudaDeviceSynchronize();
-        if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("weight repack: ") + cudaGetErrorString(e));
-    }
-    cudaFree(U32);
-    if (rc) return rc;
-    if ((rc = upload_padded(&L.mean, bn_mean, p->channels, p->Cp))) return rc;
-    if ((rc = upload_padded(&L.invstd, bn_invstd, p->channels, p->Cp))) return rc;
-    if (p->direct) {
-        rc = make_map_2d(&L.tmW, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p, p->Cp);
-        for (int ns = 1; ns <= 4 && !rc; ns++) {
-            // a channel slice must be a multiple of 64 (two epilogue warps x 32 columns)
-            if (p->Cp % ns != 0 || (p->Cp / ns) % 64 != 0) continue;
-            rc = make_map_2d(&L.tmW2[ns], p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p,
-                             p->Cp / (2 * ns));
-            L.split_ok[ns] = (rc == LZB_OK);
-        }
-        if (rc) return rc;
-    } else if (p->precision != LZB_FP32) {
-        rc = make_map_2d(&L.tmU, p->precision, L.U, (uint64_t)kPoints * p->Cp, L.cin_p, p->Cp);
-        if (rc) return rc;
-    }
-    L.present = true;
-    return LZB_OK;
+    return install_conv(p, layer, U, c_in, bn_mean, bn_invstd, false);
+}
+
+int lzb_pipe_push_conv_filters(lzb_pipe* p, int layer, const float* f, int c_in,
+                               const float* bn_mean, const float* bn_invstd) {
+    return install_conv(p, layer, f, c_in, bn_mean, bn_invstd, true);
 }
 
 int lzb_pipe_push_head_convs(lzb_pipe* p, const float* pol_w, const float* val_w) {
@@ -807,6 +856,7 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
     alloc((void**)&c->d_val, (size_t)max_batch * LZB_VAL_FLOATS * sizeof(float));
     alloc((void**)&c->d_policy, (size_t)max_batch * LZB_MOVES * sizeof(float));
     alloc((void**)&c->d_winrate, (size_t)max_batch * sizeof(float));
+    alloc((void**)&c->d_packed, (size_t)max_batch * LZB_PACKED_WORDS * sizeof(unsigned int));
     alloc((void**)&c->d_err, sizeof(int));
     if (e == cudaSuccess) e = cudaMallocHost((void**)&c->h_err, sizeof(int));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
@@ -848,7 +898,7 @@ void lzb_ctx_destroy(lzb_ctx* c) {
         cudaStreamSynchronize(c->stream);
         cudaStreamDestroy(c->stream);
     }
-    void* ptrs[] = {c->V, c->M, c->X, c->IN, c->H, c->d_in, c->d_pol, c->d_val, c->d_policy, c->d_winrate, c->d_err};
+    void* ptrs[] = {c->V, c->M, c->X, c->IN, c->H, c->d_in, c->d_pol, c->d_val, c->d_policy, c->d_winrate, c->d_packed, c->d_err};
     for (void* q : ptrs) cudaFree(q);
     if (c->h_err) cudaFreeHost(c->h_err);
     delete c;
@@ -1067,6 +1117,51 @@ int lzb_conv3x3_static(int device, const float* in_dev, int n, int c_in, int cha
     nhwc_to_nchw_kernel<float><<<128, 256, 0, stream>>>(X, out_dev, n, channels, Cp);
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
+}
+
+namespace {
+// Copy n bit-packed positions to the device and expand them into c->d_in.
+int stage_packed(lzb_ctx* c, const unsigned int* planes, int n) {
+    LZB_CUDA(cudaMemcpyAsync(c->d_packed, planes, (size_t)n * LZB_PACKED_WORDS * sizeof(unsigned int),
+                             cudaMemcpyHostToDevice, c->stream));
+    {
+        LaunchScope scope(c, kClassInput);
+        lzb::unpack_planes_kernel<<<c->pipe->sm_count * 2, 256, 0, c->stream>>>(c->d_packed, c->d_in, n);
+    }
+    LZB_CUDA(cudaGetLastError());
+    return LZB_OK;
+}
+}  // namespace
+
+int lzb_ctx_forward_packed(lzb_ctx* c, const unsigned int* planes, int n, float* pol, float* val) {
+    int rc = check_ctx(c, n);
+    if (rc) return rc;
+    if (!planes || !pol || !val) return fail(LZB_ERR_ARG, "null buffer");
+    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    if ((rc = stage_packed(c, planes, n))) return rc;
+    if ((rc = lzb_ctx_forward_device(c, c->d_in, n, c->d_pol, c->d_val))) return rc;
+    LZB_CUDA(cudaMemcpyAsync(pol, c->d_pol, (size_t)n * LZB_POL_FLOATS * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+    LZB_CUDA(cudaMemcpyAsync(val, c->d_val, (size_t)n * LZB_VAL_FLOATS * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+    return lzb_ctx_sync(c);
+}
+
+int lzb_ctx_forward_heads_packed(lzb_ctx* c, const unsigned int* planes, int n, float softmax_temp,
+                                 float* policy, float* winrate) {
+    int rc = check_ctx(c, n);
+    if (rc) return rc;
+    if (!planes || !policy || !winrate) return fail(LZB_ERR_ARG, "null buffer");
+    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    if ((rc = stage_packed(c, planes, n))) return rc;
+    if ((rc = lzb_ctx_forward_heads_device(c, c->d_in, n, softmax_temp, c->d_policy, c->d_winrate))) {
+        return rc;
+    }
+    LZB_CUDA(cudaMemcpyAsync(policy, c->d_policy, (size_t)n * LZB_MOVES * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+    LZB_CUDA(cudaMemcpyAsync(winrate, c->d_winrate, (size_t)n * sizeof(float),
+                             cudaMemcpyDeviceToHost, c->stream));
+    return lzb_ctx_sync(c);
 }
 
 int lzb_ctx_debug_wait_probe(lzb_ctx* c, int limit_ms) {

@@ -287,6 +287,49 @@ __global__ void repack_u_kernel(const float* __restrict__ U32, T* __restrict__ U
     }
 }
 
+// Filter transform on the device: f[K][c_in][3][3] -> U32[36][c_in][K] with
+// U[xi*6+nu] = (G f G^T)[xi][nu], accumulating like the reference does
+// (src/Network.cpp:159-223: acc = 0; acc += G[i][k] * f[k][j] for k = 0..2).
+__global__ void transform_f_kernel(const float* __restrict__ f, float* __restrict__ U32, int c_in,
+                                   int K) {
+    const float G[6][3] = {{1.0f, 0.0f, 0.0f},
+                           {-2.0f / 3.0f, -kSq2 / 3.0f, -1.0f / 3.0f},
+                           {-2.0f / 3.0f, kSq2 / 3.0f, -1.0f / 3.0f},
+                           {1.0f / 6.0f, kSq2 / 6.0f, 1.0f / 3.0f},
+                           {1.0f / 6.0f, -kSq2 / 6.0f, 1.0f / 3.0f},
+                           {0.0f, 0.0f, 1.0f}};
+    const int total = c_in * K;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int k = i % K, c = i / K;
+        const float* flt = f + ((size_t)k * c_in + c) * 9;
+        float gf[6][3];
+        for (int a = 0; a < 6; a++)
+            for (int j = 0; j < 3; j++) {
+                float acc = 0.0f;
+                for (int m = 0; m < 3; m++) acc = nf_add(acc, nf_mul(G[a][m], flt[m * 3 + j]));
+                gf[a][j] = acc;
+            }
+        for (int xi = 0; xi < 6; xi++)
+            for (int nu = 0; nu < 6; nu++) {
+                float acc = 0.0f;
+                for (int m = 0; m < 3; m++) acc = nf_add(acc, nf_mul(gf[xi][m], G[nu][m]));
+                U32[((size_t)(xi * 6 + nu) * c_in + c) * K + k] = acc;
+            }
+    }
+}
+
+// Bit-packed planes [n][18][12] words -> fp32 planes [n][18][361] of 0 / 1.
+__global__ void unpack_planes_kernel(const unsigned int* __restrict__ packed, float* __restrict__ out,
+                                     int n) {
+    const size_t total = (size_t)n * kInputPlanes * kSq;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int s = i % kSq;
+        const size_t plane = i / kSq;
+        out[i] = (packed[plane * 12 + (s >> 5)] >> (s & 31)) & 1u ? 1.0f : 0.0f;
+    }
+}
+
 // fp32 NCHW [n][C][361] <-> T NHWC [n][361][Cp] (diagnostics only).
 template <typename T>
 __global__ void nchw_to_nhwc_kernel(const float* __restrict__ src, T* __restrict__ dst, int n,

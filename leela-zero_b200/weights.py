@@ -164,6 +164,7 @@ def prepare(raw):
         return (np.float32(1.0) / np.sqrt(np.asarray(v, np.float32) + eps)).astype(np.float32)
 
     net = {"blocks": raw["blocks"], "channels": raw["channels"]}
+    net["filters"] = [np.ascontiguousarray(w, np.float32) for w in raw["conv_w"]]
     net["U"] = [winograd_transform_f(w) for w in raw["conv_w"]]
     net["bn_mean"] = [np.ascontiguousarray(m - b, np.float32)
                       for m, b in zip(raw["bn_mean"], raw["conv_b"])]

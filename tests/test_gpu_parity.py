@@ -317,6 +317,31 @@ def test_single_cta_and_cta_pair_kernels_agree(lzb, W, monkeypatch):
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
 
 
+def test_untransformed_filters_and_packed_positions(lzb, oracle, W):
+    """The two data formats either side of the path: filters as they stand in a
+    weights file (transformed on the GPU, or used directly by the convolution
+    kernel) and positions as bit planes.  fp32: same 1e-4 bound against the
+    oracle; packed input must reproduce the fp32-plane entry point exactly."""
+    net = W.synthetic_network(3, 64, 2059, calibrated=True)
+    x = W.synthetic_positions(9, 1059)
+    _, _, rp, rw = _reference(oracle, net, x)
+    packed = lzb.pack_positions(x)
+    assert packed.shape == (9, 18, 12) and packed.dtype == np.uint32
+    for mode, tol_p, tol_v in (("fp32", TOL_FP32, TOL_FP32), ("fp16", TOL_POLICY_16, TOL_VALUE_16),
+                               ("fp16-winograd", 1e-2, 2e-2)):
+        a = lzb.Pipe(net, mode).context(9)
+        b = lzb.Pipe(net, mode, from_filters=True).context(9)
+        pa, wa = a.forward_heads(x)
+        pb, wb = b.forward_heads(x)
+        ep, ew, l2 = _errors(oracle, pb, wb, rp, rw)
+        assert ep.max() <= tol_p and ew.max() <= tol_v and l2 <= SELFCHECK_MAX, mode
+        assert np.abs(pa - pb).max() <= tol_p and np.abs(wa - wb).max() <= tol_v, mode
+        pk, wk = a.forward_heads_packed(packed)
+        assert np.array_equal(pk, pa) and np.array_equal(wk, wa), mode
+        raw_a, raw_k = a.forward(x), a.forward_packed(packed)
+        assert np.array_equal(raw_a[0], raw_k[0]) and np.array_equal(raw_a[1], raw_k[1]), mode
+
+
 def test_device_wait_that_runs_out_is_reported_and_survivable(lzb, W):
     """Failure detection without a fault: a kernel whose barrier nobody signals
     gives up after its limit, the host sees LZB_ERR_DEVICE_WAIT (code 3) with
