@@ -1,0 +1,109 @@
+// engine_bench: the leela-zero engine (its own UCTSearch, Network, NNCache, GTP)
+// playing moves on top of CUDAPipe, to measure NN evaluations/s and playouts/s
+// end to end.  Set-up follows the engine's own start-up (src/Leela.cpp:504-519)
+// and its --benchmark settings (src/Leela.cpp:467-479); moves are requested
+// through GTP::execute("genmove ...") (src/GTP.cpp:623-690).
+//
+//   engine_bench --weights FILE [--threads T] [--batch B] [--gpus G] [--visits V]
+//                [--moves M] [--precision fp16|bf16|fp32] [--verbose]
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <iostream>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "config.h"
+
+#include "CUDAPipe.h"
+#include "GTP.h"
+#include "GameState.h"
+#include "Network.h"
+#include "Random.h"
+#include "ThreadPool.h"
+#include "UCTSearch.h"
+#include "Utils.h"
+#include "Zobrist.h"
+
+namespace lzb_engine {
+extern std::vector<int> gpus;
+extern CUDAPipe::Precision precision;
+extern std::atomic<unsigned long long> evals;
+extern CUDAPipe* last_pipe;
+}  // namespace lzb_engine
+
+int main(int argc, char** argv) {
+    std::string weights;
+    int threads = 8, batch = 8, ngpus = 1, visits = 1600, moves = 50;
+    bool verbose = false;
+    for (int i = 1; i < argc; i++) {
+        const std::string k = argv[i];
+        if (k == "--verbose") { verbose = true; continue; }
+        if (i + 1 >= argc) { std::fprintf(stderr, "missing value for %s\n", k.c_str()); return 2; }
+        const std::string v = argv[++i];
+        if (k == "--weights") weights = v;
+        else if (k == "--threads") threads = std::atoi(v.c_str());
+        else if (k == "--batch") batch = std::atoi(v.c_str());
+        else if (k == "--gpus") ngpus = std::atoi(v.c_str());
+        else if (k == "--visits") visits = std::atoi(v.c_str());
+        else if (k == "--moves") moves = std::atoi(v.c_str());
+        else if (k == "--precision") {
+            lzb_engine::precision = v == "fp32" ? CUDAPipe::Precision::FP32
+                                  : v == "bf16" ? CUDAPipe::Precision::BF16 : CUDAPipe::Precision::FP16;
+        } else { std::fprintf(stderr, "unknown option %s\n", k.c_str()); return 2; }
+    }
+    if (weights.empty()) { std::fprintf(stderr, "--weights is required\n"); return 2; }
+    lzb_engine::gpus.clear();
+    for (int g = 0; g < ngpus; g++) lzb_engine::gpus.push_back(g);
+
+    GTP::setup_default_parameters();
+    cfg_gtp_mode = true;
+    cfg_num_threads = threads;
+    cfg_batch_size = batch;
+    cfg_max_visits = visits;
+    cfg_allow_pondering = false;
+    cfg_noise = false;
+    cfg_random_cnt = 0;
+    cfg_rng_seed = 1;
+    cfg_timemanage = TimeManagement::OFF;
+    cfg_resignpct = 0;
+    cfg_quiet = !verbose;
+    cfg_weightsfile = weights;
+
+    setbuf(stdout, nullptr);
+    thread_pool.initialize(cfg_num_threads);
+    auto rng = std::make_unique<Random>(5489);
+    Zobrist::init_zobrist(*rng);
+    Random::get_Rng().seedrandom(cfg_rng_seed);
+    Utils::create_z_table();
+    {
+        auto network = std::make_unique<Network>();
+        const auto playouts = std::min(cfg_max_playouts, cfg_max_visits);
+        network->initialize(playouts, cfg_weightsfile);
+        GTP::initialize(std::move(network));
+    }
+
+    auto game = std::make_unique<GameState>();
+    game->init_game(BOARD_SIZE, KOMI);
+    game->set_timecontrol(0, 1, 0, 0);   // infinite time, as --benchmark does
+
+    const auto evals0 = lzb_engine::evals.load();
+    const auto t0 = std::chrono::steady_clock::now();
+    int played = 0;
+    for (int m = 0; m < moves; m++) {
+        GTP::execute(*game, (m % 2 == 0) ? "genmove b" : "genmove w");
+        played++;
+        if (game->get_passes() >= 2) break;
+    }
+    const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    const auto evals = lzb_engine::evals.load() - evals0;
+    const auto s = lzb_engine::last_pipe ? lzb_engine::last_pipe->stats() : CUDAPipe::Stats();
+    std::printf("\n{\"moves\": %d, \"seconds\": %.3f, \"visits_per_move\": %d, \"threads\": %d, "
+                "\"batch\": %d, \"gpus\": %d, \"nn_evals\": %llu, \"nn_evals_per_s\": %.1f, "
+                "\"visits_per_s\": %.1f, \"batches\": %zu, \"mean_batch\": %.2f, \"timeouts\": %zu}\n",
+                played, sec, visits, threads, batch, ngpus, evals, evals / sec,
+                double(played) * visits / sec, s.batches,
+                s.batches ? double(s.positions) / s.batches : 0.0, s.timeouts);
+    return 0;
+}

@@ -1,0 +1,82 @@
+"""Run the leela-zero engine on top of CUDAPipe (engine_bench) on a random-init
+network and report NN evaluations/s, visits/s and the engine's own playouts/s.
+
+    python leela-zero_b200/engine/run_engine.py --blocks 15 --filters 192 \
+        --threads 8 --batch 8 --gpus 1 --visits 1600 --moves 50
+
+The binary is built by the Makefile beside this file from the engine's own
+sources (only where the reference tree is present; the built binary is used
+otherwise).
+"""
+import argparse
+import importlib.util
+import json
+import os
+import re
+import subprocess
+import sys
+import tempfile
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.dirname(HERE)
+EXE = os.path.join(HERE, "_build", "engine_bench")
+
+
+def _weights_module():
+    spec = importlib.util.spec_from_file_location("lzb_weights", os.path.join(PKG, "weights.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def write_network(blocks, filters, seed, path):
+    """Random-init network with calibrated batch-norm statistics, v1 text format."""
+    W = _weights_module()
+    raw = W.synthetic_raw_network(blocks, filters, seed)
+    raw = W.calibrate_batchnorm(raw, W.synthetic_positions(4, seed + 1))
+    W.write_v1(raw, path)
+
+
+def run(blocks, filters, threads, batch, gpus, visits, moves, precision="fp16", seed=2004,
+        weights=None, verbose=True, timeout=3600):
+    if not os.path.exists(EXE):
+        raise RuntimeError("%s is missing: make -C %s (needs the reference tree)" % (EXE, HERE))
+    tmp = None
+    if weights is None:
+        tmp = tempfile.NamedTemporaryFile(suffix=".txt.gz", delete=False)
+        tmp.close()
+        weights = tmp.name
+        write_network(blocks, filters, seed, weights)
+    cmd = [EXE, "--weights", weights, "--threads", str(threads), "--batch", str(batch), "--gpus",
+           str(gpus), "--visits", str(visits), "--moves", str(moves), "--precision", precision]
+    if verbose:
+        cmd.append("--verbose")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    if tmp is not None:
+        os.unlink(weights)
+    if r.returncode != 0:
+        raise RuntimeError("engine_bench failed (%d): %s" % (r.returncode, r.stderr[-2000:]))
+    summary = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    summary["gtp_moves"] = re.findall(r"^= (\S+)", r.stdout, flags=re.M)
+    # the engine's own per-move line: "<visits> visits, <nodes> nodes, <playouts> playouts, <n/s> n/s"
+    rates = [(int(a), int(b)) for a, b in re.findall(r"(\d+) playouts, (\d+) n/s", r.stderr)]
+    if rates:
+        summary["engine_playouts"] = sum(a for a, _ in rates)
+        summary["engine_playouts_per_s_mean"] = sum(b for _, b in rates) / len(rates)
+    return summary
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--blocks", type=int, default=15)
+    ap.add_argument("--filters", type=int, default=192)
+    ap.add_argument("--threads", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--visits", type=int, default=1600)
+    ap.add_argument("--moves", type=int, default=50)
+    ap.add_argument("--precision", default="fp16")
+    ap.add_argument("--weights", default=None)
+    a = ap.parse_args()
+    print(json.dumps(run(a.blocks, a.filters, a.threads, a.batch, a.gpus, a.visits, a.moves,
+                         a.precision, weights=a.weights)))

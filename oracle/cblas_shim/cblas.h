@@ -17,6 +17,7 @@ void cblas_sgemv(enum CBLAS_ORDER order, enum CBLAS_TRANSPOSE ta, int m, int n,
                  float alpha, const float* a, int lda, const float* x, int incx,
                  float beta, float* y, int incy);
 void openblas_set_num_threads(int n);
+char* openblas_get_corename(void);
 #ifdef __cplusplus
 }
 #endif
