@@ -223,7 +223,19 @@ def main():
 
     pkg = load_package()
     W = pkg.weights
-    net = W.synthetic_network(BLOCKS, FILTERS, WEIGHT_SEED, calibrated=True)
+    # Every rank draws the same raw network from the seed; the batch-norm
+    # calibration pass (a few seconds of CPU) runs on rank 0 only and its
+    # statistics are handed to the other ranks.
+    raw = W.synthetic_raw_network(BLOCKS, FILTERS, WEIGHT_SEED)
+    bn_keys = ("bn_mean", "bn_var", "bn_pol_mean", "bn_pol_var", "bn_val_mean", "bn_val_var")
+    stats = [None]
+    if rank == 0:
+        cal = W.calibrate_batchnorm(raw, W.synthetic_positions(4, WEIGHT_SEED + 1))
+        stats = [{k: cal[k] for k in bn_keys}]
+    if world > 1:
+        dist.broadcast_object_list(stats, src=0)
+    raw.update(stats[0])
+    net = W.prepare(raw)
     pipe = pkg.Pipe(net, args.precision, device=local)
     B = args.batch
     ctx = pipe.context(B)

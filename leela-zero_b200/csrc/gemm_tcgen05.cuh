@@ -216,6 +216,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 20 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 4; i++) {
@@ -243,6 +244,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_tc_kernel(
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // launched with programmatic stream serialization: the set-up above overlaps
+    // the tail of the previous kernel, V is only read after it has finished
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // V was written with ordinary stores and is read here by TMA (async proxy)
+    asm volatile("fence.proxy.async;" ::: "memory");
 
     const int items = 36 * nblk;   // 36 Winograd points
     const int item_begin = static_cast<int>(static_cast<long long>(blockIdx.x) * items / gridDim.x);

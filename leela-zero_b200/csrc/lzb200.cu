@@ -43,12 +43,23 @@ int fail(int code, const std::string& msg) {
     do {                                                                                   \
         cudaError_t e_ = (expr);                                                           \
         if (e_ != cudaSuccess) {                                                           \
+            (void)cudaGetLastError(); /* reported here: do not leave it for a later check */ \
             return fail(LZB_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e_)); \
         }                                                                                  \
     } while (0)
 
+// Select the device and drop any error an earlier call (of this library or of
+// another one in the process) left behind, so that the cudaGetLastError() after
+// a kernel launch reports that launch and nothing older.
+inline cudaError_t enter_device(int device) {
+    const cudaError_t e = cudaSetDevice(device);
+    (void)cudaGetLastError();
+    return e;
+}
+
 inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
+constexpr int kXformSmem = lzb::kBoardCells * 32 * 8;   // fp32 board of one position x 64 channels
 constexpr int kMaxMicroBatch = 256;      // rows of V/M allocated: 25 * 256 = 6400
 constexpr int kDefaultMicroBatch = 64;
 
@@ -253,12 +264,24 @@ int launch_gemm_tc(lzb_ctx* c, const Layer& L, int P, bool first) {
     const int nblk = (P + tc::kBlockM - 1) / tc::kBlockM;
     const int items = kPoints * nblk;
     const int grid = items < p->sm_count ? items : p->sm_count;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(tc::kThreads);
+    cfg.dynamicSmemBytes = tc::kSmemBytes;
+    cfg.stream = c->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le;
     {
         LaunchScope scope(c, kClassContraction);
-        tc::gemm_tc_kernel<T><<<grid, tc::kThreads, tc::kSmemBytes, c->stream>>>(
-            first ? c->tmV_first : c->tmV, L.tmU, static_cast<T*>(c->M), c->Pa, P, p->Cp,
-            L.cin_p / tc::kChunkK, nblk, c->d_err);
+        le = cudaLaunchKernelEx(&cfg, tc::gemm_tc_kernel<T>, first ? c->tmV_first : c->tmV, L.tmU,
+                                static_cast<T*>(c->M), c->Pa, P, p->Cp, L.cin_p / tc::kChunkK, nblk,
+                                c->d_err);
     }
+    LZB_CUDA(le);
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }
@@ -277,12 +300,23 @@ template <typename T>
 int launch_xform(lzb_ctx* c, const Layer& L, int nb, const T* R, T* X_out, T* V) {
     lzb_pipe* p = c->pipe;
     const dim3 grid(p->Cp / kChanPerCta, nb);
-    const size_t smem = (size_t)kBoardCells * 32 * 2 * sizeof(T);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(XformShape<T>::warps * 32);
+    cfg.dynamicSmemBytes = kXformSmem;
+    cfg.stream = c->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le;
     {
         LaunchScope scope(c, kClassTransform);
-        xform_kernel<T><<<grid, kXformThreads, smem, c->stream>>>(
-            static_cast<const T*>(c->M), c->Pa, p->Cp, L.mean, L.invstd, R, X_out, V);
+        le = cudaLaunchKernelEx(&cfg, xform_kernel<T>, static_cast<const T*>(c->M), c->Pa, p->Cp,
+                                (const float*)L.mean, (const float*)L.invstd, R, X_out, V);
     }
+    LZB_CUDA(le);
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
 }
@@ -431,21 +465,21 @@ int check_ctx(lzb_ctx* c, int n) {
 
 int set_smem_attrs() {
     LZB_CUDA(cudaFuncSetAttribute(xform_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kBoardCells * 32 * 2 * 4));
+                                  kXformSmem));
     LZB_CUDA(cudaFuncSetAttribute(in_transform_kernel<float>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kBoardCells * 32 * 2 * 4));
+                                  kXformSmem));
     LZB_CUDA(cudaFuncSetAttribute(xform_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kBoardCells * 32 * 2 * 2));
+                                  kXformSmem));
     LZB_CUDA(cudaFuncSetAttribute(xform_kernel<__nv_bfloat16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kBoardCells * 32 * 2 * 2));
+                                  kXformSmem));
     LZB_CUDA(cudaFuncSetAttribute(in_transform_kernel<__half>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kBoardCells * 32 * 2 * 2));
+                                  kXformSmem));
     LZB_CUDA(cudaFuncSetAttribute(in_transform_kernel<__nv_bfloat16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kBoardCells * 32 * 2 * 2));
+                                  kXformSmem));
     LZB_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<__half>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kSmemBytes));
     LZB_CUDA(cudaFuncSetAttribute(tc::gemm_tc_kernel<__nv_bfloat16>,
@@ -530,7 +564,7 @@ int debug_conv_t(lzb_ctx* c, int layer, const float* in, int n, const float* res
         guard(cudaMemcpyAsync(stage, in, sizeof(float) * plane_floats, cudaMemcpyHostToDevice, c->stream), "copy in");
         nchw_to_nhwc_kernel<T><<<512, 256, 0, c->stream>>>(stage, X, n, C, p->Cp);
         const dim3 grid(p->Cp / kChanPerCta, n);
-        in_transform_kernel<T><<<grid, kXformThreads, (size_t)kBoardCells * 32 * 2 * sizeof(T), c->stream>>>(
+        in_transform_kernel<T><<<grid, kXformThreads, kXformSmem, c->stream>>>(
             X, V, c->Pa, p->Cp);
     }
     guard(cudaGetLastError(), "input transform");
@@ -587,7 +621,7 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
     if (layer < 0 || layer >= (int)p->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
     const int want = layer == 0 ? kInputPlanes : p->channels;
     if (c_in != want) return fail(LZB_ERR_ARG, "c_in does not match the layer");
-    LZB_CUDA(cudaSetDevice(p->device));
+    LZB_CUDA(enter_device(p->device));
     Layer& L = p->layers[layer];
     if (L.present) return fail(LZB_ERR_ARG, "layer pushed twice");
     L.cin_p = round_up(c_in, 64);
@@ -714,7 +748,7 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     if (precision != LZB_FP32 && Cp > tc::kMaxN) {
         return fail(LZB_ERR_ARG, "tensor-core path supports at most 256 filters; use LZB_FP32");
     }
-    LZB_CUDA(cudaSetDevice(device));
+    LZB_CUDA(enter_device(device));
     cudaDeviceProp prop;
     LZB_CUDA(cudaGetDeviceProperties(&prop, device));
     if (prop.major != 10) {
@@ -770,7 +804,7 @@ int lzb_pipe_push_conv_filters(lzb_pipe* p, int layer, const float* f, int c_in,
 int lzb_pipe_push_head_convs(lzb_pipe* p, const float* pol_w, const float* val_w) {
     if (!p || !pol_w || !val_w) return fail(LZB_ERR_ARG, "null argument");
     if (p->finalized) return fail(LZB_ERR_ARG, "pipe already finalized");
-    LZB_CUDA(cudaSetDevice(p->device));
+    LZB_CUDA(enter_device(p->device));
     std::vector<float> w((size_t)3 * p->Cp, 0.0f);
     for (int c = 0; c < p->channels; c++) {
         w[c] = pol_w[c];
@@ -793,7 +827,7 @@ int lzb_pipe_push_heads(lzb_pipe* p, const float* bn_pol_mean, const float* bn_p
         return fail(LZB_ERR_ARG, "null argument");
     }
     if (p->heads.present) return fail(LZB_ERR_ARG, "heads pushed twice");
-    LZB_CUDA(cudaSetDevice(p->device));
+    LZB_CUDA(enter_device(p->device));
     Heads& h = p->heads;
     int rc;
     if ((rc = upload_plain(&h.bn_pol_mean, bn_pol_mean, 2))) return rc;
@@ -825,7 +859,7 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
     *out = nullptr;
     if (!p || !p->finalized) return fail(LZB_ERR_ARG, "pipe not finalized");
     if (max_batch < 1 || max_batch > (1 << 16)) return fail(LZB_ERR_ARG, "bad max_batch");
-    LZB_CUDA(cudaSetDevice(p->device));
+    LZB_CUDA(enter_device(p->device));
     lzb_ctx* c = new lzb_ctx;
     c->pipe = p;
     c->max_batch = max_batch;
@@ -920,7 +954,7 @@ int lzb_ctx_forward_device(lzb_ctx* c, const float* in_dev, int n, float* pol_de
     int rc = check_ctx(c, n);
     if (rc) return rc;
     if (!in_dev || !pol_dev || !val_dev) return fail(LZB_ERR_ARG, "null buffer");
-    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(enter_device(c->pipe->device));
     for (int off = 0; off < n; off += c->micro) {
         const int nb = (n - off) < c->micro ? (n - off) : c->micro;
         rc = run_tower_any(c, in_dev + (size_t)off * LZB_IN_FLOATS, nb,
@@ -933,7 +967,7 @@ int lzb_ctx_forward_device(lzb_ctx* c, const float* in_dev, int n, float* pol_de
 
 int lzb_ctx_sync(lzb_ctx* c) {
     if (!c) return fail(LZB_ERR_ARG, "null context");
-    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(enter_device(c->pipe->device));
     LZB_CUDA(cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
     LZB_CUDA(cudaStreamSynchronize(c->stream));
     if (*c->h_err != 0) {
@@ -950,7 +984,7 @@ int lzb_ctx_forward(lzb_ctx* c, const float* in, int n, float* pol, float* val) 
     int rc = check_ctx(c, n);
     if (rc) return rc;
     if (!in || !pol || !val) return fail(LZB_ERR_ARG, "null buffer");
-    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(enter_device(c->pipe->device));
     LZB_CUDA(cudaMemcpyAsync(c->d_in, in, (size_t)n * LZB_IN_FLOATS * sizeof(float),
                              cudaMemcpyHostToDevice, c->stream));
     if ((rc = lzb_ctx_forward_device(c, c->d_in, n, c->d_pol, c->d_val))) return rc;
@@ -991,7 +1025,7 @@ int lzb_ctx_forward_heads(lzb_ctx* c, const float* in, int n, float softmax_temp
     int rc = check_ctx(c, n);
     if (rc) return rc;
     if (!in || !policy || !winrate) return fail(LZB_ERR_ARG, "null buffer");
-    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(enter_device(c->pipe->device));
     LZB_CUDA(cudaMemcpyAsync(c->d_in, in, (size_t)n * LZB_IN_FLOATS * sizeof(float),
                              cudaMemcpyHostToDevice, c->stream));
     if ((rc = lzb_ctx_forward_heads_device(c, c->d_in, n, softmax_temp, c->d_policy, c->d_winrate))) {
@@ -1049,11 +1083,11 @@ int static_scratch_for(int device, unsigned char** out) {
                                           cudaGetErrorString(e));
         }
         e = cudaFuncSetAttribute(lzb::xform_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 lzb::kBoardCells * 32 * 2 * 4);
+                                 kXformSmem);
         if (e == cudaSuccess) {
             e = cudaFuncSetAttribute(lzb::in_transform_kernel<float>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     lzb::kBoardCells * 32 * 2 * 4);
+                                     kXformSmem);
         }
         if (e != cudaSuccess) {
             return fail(LZB_ERR_CUDA, std::string("kernel attribute set-up: ") + cudaGetErrorString(e));
@@ -1082,7 +1116,7 @@ int lzb_conv3x3_static(int device, const float* in_dev, int n, int c_in, int cha
                                      std::to_string(kStaticMaxChannels) + " input and output channels, got " +
                                      std::to_string(c_in) + " and " + std::to_string(channels));
     }
-    LZB_CUDA(cudaSetDevice(device));
+    LZB_CUDA(enter_device(device));
     unsigned char* scratch = nullptr;
     int rc = static_scratch_for(device, &scratch);
     if (rc) return rc;
@@ -1103,7 +1137,7 @@ int lzb_conv3x3_static(int device, const float* in_dev, int n, int c_in, int cha
     repack_u_kernel<float><<<144, 256, 0, stream>>>(U_dev, U, c_in, channels, Cp, Cp);
     nchw_to_nhwc_kernel<float><<<128, 256, 0, stream>>>(in_dev, X, n, c_in, Cp);
     const dim3 tgrid(Cp / kChanPerCta, n);
-    const size_t tsmem = (size_t)kBoardCells * 32 * 2 * sizeof(float);
+    const size_t tsmem = kXformSmem;
     in_transform_kernel<float><<<tgrid, kXformThreads, tsmem, stream>>>(X, V, kStaticRows, Cp);
     const dim3 ggrid(round_up(P, kSimtTile) / kSimtTile, Cp / kSimtTile, kPoints);
     gemm_f32_kernel<<<ggrid, 256, 0, stream>>>(V, U, M, kStaticRows, Cp, Cp);
@@ -1112,7 +1146,7 @@ int lzb_conv3x3_static(int device, const float* in_dev, int n, int c_in, int cha
         nchw_to_nhwc_kernel<float><<<128, 256, 0, stream>>>(residual_dev, X, n, channels, Cp);
         R = X;
     }
-    xform_kernel<float><<<tgrid, kXformThreads, tsmem, stream>>>(M, kStaticRows, Cp, bn, bn + 64, R, X,
+    xform_kernel<float><<<tgrid, XformShape<float>::warps * 32, tsmem, stream>>>(M, kStaticRows, Cp, bn, bn + 64, R, X,
                                                                   nullptr);
     nhwc_to_nchw_kernel<float><<<128, 256, 0, stream>>>(X, out_dev, n, channels, Cp);
     LZB_CUDA(cudaGetLastError());
@@ -1137,7 +1171,7 @@ int lzb_ctx_forward_packed(lzb_ctx* c, const unsigned int* planes, int n, float*
     int rc = check_ctx(c, n);
     if (rc) return rc;
     if (!planes || !pol || !val) return fail(LZB_ERR_ARG, "null buffer");
-    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(enter_device(c->pipe->device));
     if ((rc = stage_packed(c, planes, n))) return rc;
     if ((rc = lzb_ctx_forward_device(c, c->d_in, n, c->d_pol, c->d_val))) return rc;
     LZB_CUDA(cudaMemcpyAsync(pol, c->d_pol, (size_t)n * LZB_POL_FLOATS * sizeof(float),
@@ -1152,7 +1186,7 @@ int lzb_ctx_forward_heads_packed(lzb_ctx* c, const unsigned int* planes, int n, 
     int rc = check_ctx(c, n);
     if (rc) return rc;
     if (!planes || !policy || !winrate) return fail(LZB_ERR_ARG, "null buffer");
-    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(enter_device(c->pipe->device));
     if ((rc = stage_packed(c, planes, n))) return rc;
     if ((rc = lzb_ctx_forward_heads_device(c, c->d_in, n, softmax_temp, c->d_policy, c->d_winrate))) {
         return rc;
@@ -1167,7 +1201,7 @@ int lzb_ctx_forward_heads_packed(lzb_ctx* c, const unsigned int* planes, int n, 
 int lzb_ctx_debug_wait_probe(lzb_ctx* c, int limit_ms) {
     if (!c) return fail(LZB_ERR_ARG, "null context");
     if (limit_ms < 1 || limit_ms > 1000) return fail(LZB_ERR_ARG, "limit must be 1..1000 ms");
-    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(enter_device(c->pipe->device));
     wait_probe_kernel<<<1, 32, 0, c->stream>>>(c->d_err, (unsigned long long)limit_ms * 1000000ull);
     c->launches++;
     LZB_CUDA(cudaGetLastError());
@@ -1210,7 +1244,7 @@ int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n, const floa
     if (n < 1 || n > c->micro_cap) return fail(LZB_ERR_ARG, "batch outside the micro-batch capacity");
     if (layer < 0 || layer >= (int)c->pipe->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
     if (!in || !out) return fail(LZB_ERR_ARG, "null buffer");
-    LZB_CUDA(cudaSetDevice(c->pipe->device));
+    LZB_CUDA(enter_device(c->pipe->device));
     if (c->pipe->direct) {
         return c->pipe->precision == LZB_FP16
                    ? debug_conv_direct_t<__half>(c, layer, in, n, residual, out)

@@ -21,12 +21,18 @@ constexpr int kBoardPad = 22;                 // 2 + 4 * 5 : cells -1 .. 20
 constexpr int kBoardCells = kBoardPad * kBoardPad;
 constexpr int kXformWarps = 8;
 constexpr int kXformThreads = kXformWarps * 32;
+// The fused transform runs one warp per tile in the 16-bit modes (25 warps: all
+// 25 tiles of a position have their loads in flight at once; the kernel is
+// bound by L2 latency, not by arithmetic) and 8 warps in fp32, whose 124 KB
+// board leaves room for one CTA per SM anyway.
+template <typename T> struct XformShape { static constexpr int warps = 25; static constexpr int ctas = 1; };
+template <> struct XformShape<float> { static constexpr int warps = 8; static constexpr int ctas = 1; };
 constexpr int kChanPerCta = 64;               // one warp covers 32 channel pairs
 
 // B^T d B of the 6x6 patch of tile (by, bx), read from a zero-haloed board in
 // shared memory, written to V rows of point t = xi*6 + nu.
 template <typename T>
-__device__ __forceinline__ void tile_in_transform(const typename Pair<T>::type* board,
+__device__ __forceinline__ void tile_in_transform(const float2* board,
                                                   int lane, int by, int bx,
                                                   T* V, size_t v_row_stride_pts,
                                                   size_t v_off) {
@@ -37,16 +43,16 @@ __device__ __forceinline__ void tile_in_transform(const typename Pair<T>::type* 
         float2 vin[6], vout[6];
 #pragma unroll
         for (int r = 0; r < 6; r++) {
-            vin[r] = P2::to_f2(board[((4 * by + r) * kBoardPad + 4 * bx + col) * 32 + lane]);
+            vin[r] = board[((4 * by + r) * kBoardPad + 4 * bx + col) * 32 + lane];
         }
-        apply_bt(vout, vin);
+        apply_bt<Pair<T>::exact>(vout, vin);
 #pragma unroll
         for (int r = 0; r < 6; r++) t1[r][col] = vout[r];
     }
 #pragma unroll
     for (int xi = 0; xi < 6; xi++) {
         float2 vout[6];
-        apply_bt(vout, t1[xi]);
+        apply_bt<Pair<T>::exact>(vout, t1[xi]);
 #pragma unroll
         for (int nu = 0; nu < 6; nu++) {
             auto* dst = reinterpret_cast<typename P2::type*>(
@@ -56,13 +62,11 @@ __device__ __forceinline__ void tile_in_transform(const typename Pair<T>::type* 
     }
 }
 
-template <typename T>
-__device__ __forceinline__ void zero_halo(typename Pair<T>::type* board, int warp, int lane,
-                                          int nwarps) {
+__device__ __forceinline__ void zero_halo(float2* board, int warp, int lane, int nwarps) {
     for (int cell = warp; cell < kBoardCells; cell += nwarps) {
         const int r = cell / kBoardPad, c = cell % kBoardPad;
         if (r == 0 || r > kBoard || c == 0 || c > kBoard) {
-            board[cell * 32 + lane] = Pair<T>::zero();
+            board[cell * 32 + lane] = make_float2(0.f, 0.f);
         }
     }
 }
@@ -98,14 +102,14 @@ __global__ void __launch_bounds__(256) first_in_transform_kernel(
             vin[r] = inside ? make_float2(pl0[y * kBoard + x], pl1[y * kBoard + x])
                             : make_float2(0.f, 0.f);
         }
-        apply_bt(vout, vin);
+        apply_bt<Pair<T>::exact>(vout, vin);
 #pragma unroll
         for (int r = 0; r < 6; r++) t1[r][col] = vout[r];
     }
 #pragma unroll
     for (int xi = 0; xi < 6; xi++) {
         float2 vout[6];
-        apply_bt(vout, t1[xi]);
+        apply_bt<Pair<T>::exact>(vout, t1[xi]);
 #pragma unroll
         for (int nu = 0; nu < 6; nu++) {
             auto* dst = reinterpret_cast<typename P2::type*>(
@@ -126,14 +130,14 @@ __global__ void __launch_bounds__(kXformThreads) in_transform_kernel(
     const T* __restrict__ X, T* __restrict__ V, int Pa, int Cp) {
     using P2 = Pair<T>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    auto* board = reinterpret_cast<typename P2::type*>(smem_raw);
+    auto* board = reinterpret_cast<float2*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.y, k = blockIdx.x * kChanPerCta + 2 * lane;
-    zero_halo<T>(board, warp, lane, kXformWarps);
+    zero_halo(board, warp, lane, kXformWarps);
     for (int s = warp; s < kSq; s += kXformWarps) {
         const int y = s / kBoard, x = s % kBoard;
         board[((y + 1) * kBoardPad + x + 1) * 32 + lane] =
-            *reinterpret_cast<const typename P2::type*>(X + ((size_t)n * kSq + s) * Cp + k);
+            P2::to_f2(*reinterpret_cast<const typename P2::type*>(X + ((size_t)n * kSq + s) * Cp + k));
     }
     __syncthreads();
     for (int tile = warp; tile < kTilesPerPos; tile += kXformWarps) {
@@ -152,26 +156,30 @@ __global__ void __launch_bounds__(kXformThreads) in_transform_kernel(
 // activations never travel through global memory unless they are needed later
 // as a residual.  R and X_out may be the same buffer: every element is read
 // and written by the same thread.
-// grid (Cp/64, n), block 256, dynamic smem = 484 * 32 * sizeof(pair).
+// grid (Cp/64, n), block XformShape<T>::warps * 32, dynamic smem = 484 * 32 * 8 bytes (fp32 board).
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(kXformThreads, 2) xform_kernel(
-    const T* __restrict__ M, int Pa, int Cp,
+__global__ void __launch_bounds__(XformShape<T>::warps * 32, XformShape<T>::ctas) xform_kernel(
+    const T* M, int Pa, int Cp,
     const float* __restrict__ bn_mean, const float* __restrict__ bn_invstd,
     const T* R, T* X_out, T* __restrict__ V) {
     using P2 = Pair<T>;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    auto* board = reinterpret_cast<typename P2::type*>(smem_raw);
+    auto* board = reinterpret_cast<float2*>(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.y, k = blockIdx.x * kChanPerCta + 2 * lane;
     const size_t pt_stride = (size_t)Pa * Cp;
 
-    if (V != nullptr) zero_halo<T>(board, warp, lane, kXformWarps);
+    // launched with programmatic stream serialization: let the next kernel set
+    // up, prepare what does not depend on the previous one, then wait for it
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (V != nullptr) zero_halo(board, warp, lane, XformShape<T>::warps);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const float2 mean = *reinterpret_cast<const float2*>(bn_mean + k);
     const float2 scale = *reinterpret_cast<const float2*>(bn_invstd + k);
 
-    for (int tile = warp; tile < kTilesPerPos; tile += kXformWarps) {
+    for (int tile = warp; tile < kTilesPerPos; tile += XformShape<T>::warps) {
         const int by = tile / kTilesPerSide, bx = tile % kTilesPerSide;
         const T* msrc = M + (size_t)(n * kTilesPerPos + tile) * Cp + k;
         // temp[i][nu] = sum_xi At[i][xi] m[xi][nu]
@@ -181,17 +189,19 @@ __global__ void __launch_bounds__(kXformThreads, 2) xform_kernel(
             float2 colv[6], o4[4];
 #pragma unroll
             for (int xi = 0; xi < 6; xi++) {
-                colv[xi] = P2::to_f2(*reinterpret_cast<const typename P2::type*>(
-                    msrc + (size_t)(xi * 6 + nu) * pt_stride));
+                // M is still being written when this kernel starts, so it is
+                // not read-only for the kernel's lifetime: no ld.global.nc
+                colv[xi] = P2::to_f2(__ldcg(reinterpret_cast<const typename P2::type*>(
+                    msrc + (size_t)(xi * 6 + nu) * pt_stride)));
             }
-            apply_at(o4, colv);
+            apply_at<Pair<T>::exact>(o4, colv);
 #pragma unroll
             for (int i = 0; i < 4; i++) temp[i][nu] = o4[i];
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             float2 o4[4];
-            apply_at(o4, temp[i]);
+            apply_at<Pair<T>::exact>(o4, temp[i]);
             const int y = 4 * by + i;
             if (y >= kBoard) continue;
 #pragma unroll
@@ -199,12 +209,13 @@ __global__ void __launch_bounds__(kXformThreads, 2) xform_kernel(
                 const int x = 4 * bx + j;
                 if (x >= kBoard) continue;
                 // max(0, invstd * (v - mean) [+ residual]), src/CPUPipe.cpp:352-377
-                float2 v = make_float2(nf_mul(scale.x, nf_add(o4[j].x, -mean.x)),
-                                       nf_mul(scale.y, nf_add(o4[j].y, -mean.y)));
+                constexpr bool kE = Pair<T>::exact;
+                float2 v = make_float2(op_mul<kE>(scale.x, op_add<kE>(o4[j].x, -mean.x)),
+                                       op_mul<kE>(scale.y, op_add<kE>(o4[j].y, -mean.y)));
                 const size_t xoff = ((size_t)n * kSq + y * kBoard + x) * Cp + k;
                 if (R != nullptr) {
                     const float2 r = P2::to_f2(*reinterpret_cast<const typename P2::type*>(R + xoff));
-                    v = add2(v, r);
+                    v = add2<Pair<T>::exact>(v, r);
                 }
                 v.x = fmaxf(v.x, 0.f);
                 v.y = fmaxf(v.y, 0.f);
@@ -213,14 +224,14 @@ __global__ void __launch_bounds__(kXformThreads, 2) xform_kernel(
                     *reinterpret_cast<typename P2::type*>(X_out + xoff) = packed;
                 }
                 if (V != nullptr) {
-                    board[((y + 1) * kBoardPad + x + 1) * 32 + lane] = packed;
+                    board[((y + 1) * kBoardPad + x + 1) * 32 + lane] = v;
                 }
             }
         }
     }
     if (V == nullptr) return;
     __syncthreads();
-    for (int tile = warp; tile < kTilesPerPos; tile += kXformWarps) {
+    for (int tile = warp; tile < kTilesPerPos; tile += XformShape<T>::warps) {
         const int p = n * kTilesPerPos + tile;
         tile_in_transform<T>(board, lane, tile / kTilesPerSide, tile % kTilesPerSide, V,
                              pt_stride, (size_t)p * Cp + k);
