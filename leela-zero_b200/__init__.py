@@ -118,6 +118,8 @@ class Pipe:
     ``push_weights`` (src/ForwardPipe.h:40-54): ``U`` (list of fp32
     ``[36][c_in][C]``), ``bn_mean``, ``bn_invstd`` (lists of ``[C]``),
     ``pol_w`` ``[2][C]``, ``val_w`` ``[1][C]``, plus optionally ``heads``.
+    With ``from_filters`` the layers come from ``net["filters"]`` (untransformed
+    ``[C][c_in][3][3]``, as ``weights.load_network`` returns them) instead of ``U``.
     """
 
     def __init__(self, net, precision="fp16", device=0, heads=True, from_filters=False):
@@ -127,14 +129,14 @@ class Pipe:
         self.precision = PRECISIONS[precision] if isinstance(precision, str) else precision
         check(L.lzb_pipe_create(ctypes.byref(self.h), device, self.channels, self.blocks,
                                 self.precision))
-        for l, U in enumerate(net["U"]):
+        for l in range(len(net["bn_mean"])):
             mean = _ptr(np.ascontiguousarray(net["bn_mean"][l], np.float32))
             inv = _ptr(np.ascontiguousarray(net["bn_invstd"][l], np.float32))
             if from_filters:      # untransformed filters [K][c_in][3][3], as in a weights file
                 f = np.ascontiguousarray(net["filters"][l], np.float32)
                 check(L.lzb_pipe_push_conv_filters(self.h, l, _ptr(f), f.shape[1], mean, inv))
             else:                 # Winograd-transformed, as the engine hands them to a pipe
-                U = np.ascontiguousarray(U, np.float32)
+                U = np.ascontiguousarray(net["U"][l], np.float32)
                 check(L.lzb_pipe_push_conv(self.h, l, _ptr(U), U.shape[1], mean, inv))
         check(L.lzb_pipe_push_head_convs(self.h, _ptr(np.ascontiguousarray(net["pol_w"], np.float32)),
                                          _ptr(np.ascontiguousarray(net["val_w"], np.float32))))

@@ -154,10 +154,12 @@ def winograd_transform_f(f):
     return np.ascontiguousarray(u.reshape(36, C, K))
 
 
-def prepare(raw):
+def prepare(raw, transform=True):
     """What ``Network::initialize`` does to a loaded file before a pipe sees
     it (src/Network.cpp:540-576): Winograd-transform every 3x3 filter,
-    var -> 1/sqrt(var + 1e-5), fold conv biases into the BN means."""
+    var -> 1/sqrt(var + 1e-5), fold conv biases into the BN means.  With
+    ``transform=False`` the filter transform is left to the GPU (the pipe is
+    then built with ``from_filters=True``) and ``U`` holds ``None``."""
     eps = np.float32(1e-5)
 
     def invstd(v):
@@ -165,7 +167,8 @@ def prepare(raw):
 
     net = {"blocks": raw["blocks"], "channels": raw["channels"]}
     net["filters"] = [np.ascontiguousarray(w, np.float32) for w in raw["conv_w"]]
-    net["U"] = [winograd_transform_f(w) for w in raw["conv_w"]]
+    net["version"] = raw.get("version", 1)   # 2: value head from black's view (src/Network.cpp:393-400)
+    net["U"] = [winograd_transform_f(w) if transform else None for w in raw["conv_w"]]
     net["bn_mean"] = [np.ascontiguousarray(m - b, np.float32)
                       for m, b in zip(raw["bn_mean"], raw["conv_b"])]
     net["bn_invstd"] = [invstd(v) for v in raw["bn_var"]]
@@ -184,6 +187,52 @@ def prepare(raw):
         "ip2_val_b": np.ascontiguousarray(raw["ip2_val_b"], np.float32),
     }
     return net
+
+
+_CACHE_KEYS = ("conv_w", "conv_b", "bn_mean", "bn_var")
+
+
+def load_network(path, cache_dir=None):
+    """Weights file -> network dict for ``Pipe(net, ..., from_filters=True)``.
+
+    The text format is slow to parse (a 40 x 256 network is about 1.7 GB of
+    decimal text), so with ``cache_dir`` the parsed fp32 arrays are kept there
+    as ``<sha256 of the file bytes>.npz`` and the next load of the same file
+    reads that instead.  The 3x3 filters stay untransformed: the pipe runs the
+    filter transform (src/Network.cpp:159-223) on the GPU at upload."""
+    import hashlib
+    import os
+    cached = None
+    if cache_dir is not None:
+        h = hashlib.sha256()
+        with open(path, "rb") as f:
+            for chunk in iter(lambda: f.read(1 << 22), b""):
+                h.update(chunk)
+        cached = os.path.join(cache_dir, h.hexdigest() + ".npz")
+    if cached is not None and os.path.exists(cached):
+        z = np.load(cached)
+        raw = {"blocks": int(z["blocks"]), "channels": int(z["channels"]),
+               "version": int(z["version"])}
+        nconv = 1 + 2 * raw["blocks"]
+        for k in _CACHE_KEYS:
+            raw[k] = [z["%s/%d" % (k, l)] for l in range(nconv)]
+        for k in _HEAD_ORDER:
+            raw[k] = z[k]
+    else:
+        raw = read_v1(path)
+        if cached is not None:
+            os.makedirs(cache_dir, exist_ok=True)
+            arrays = {"blocks": raw["blocks"], "channels": raw["channels"],
+                      "version": raw["version"]}
+            for k in _CACHE_KEYS:
+                for l, a in enumerate(raw[k]):
+                    arrays["%s/%d" % (k, l)] = a
+            for k in _HEAD_ORDER:
+                arrays[k] = raw[k]
+            tmp = cached + ".tmp%d.npz" % os.getpid()
+            np.savez(tmp, **arrays)
+            os.replace(tmp, cached)      # readers never see a half-written cache file
+    return prepare(raw, transform=False)
 
 
 def conv3x3_direct(x, w):

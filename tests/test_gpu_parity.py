@@ -344,6 +344,22 @@ def test_untransformed_filters_and_packed_positions(lzb, oracle, W):
         assert np.array_equal(raw_a[0], raw_k[0]) and np.array_equal(raw_a[1], raw_k[1]), mode
 
 
+def test_weights_file_to_pipe(lzb, oracle, W, tmp_path):
+    """A gzip'd v1 weights file through the cached loader and the GPU-side
+    filter transform gives the oracle's outputs (fp32, 1e-4), from the first
+    parse and from the cache alike."""
+    raw = W.synthetic_raw_network(2, 32, 2060)
+    path = str(tmp_path / "net.txt.gz")
+    W.write_v1(raw, path)
+    x = W.synthetic_positions(3, 1060)
+    _, _, rp, rw = _reference(oracle, W.prepare(W.read_v1(path)), x)
+    for _ in range(2):
+        net = W.load_network(path, str(tmp_path / "cache"))
+        policy, win = lzb.Pipe(net, "fp32", from_filters=True).context(3).forward_heads(x)
+        ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
+        assert ep.max() <= TOL_FP32 and ew.max() <= TOL_FP32
+
+
 def test_device_wait_that_runs_out_is_reported_and_survivable(lzb, W):
     """Failure detection without a fault: a kernel whose barrier nobody signals
     gives up after its limit, the host sees LZB_ERR_DEVICE_WAIT (code 3) with

@@ -115,6 +115,36 @@ def test_v1_file_round_trip(W, tmp_path):
             assert np.array_equal(back[k].ravel(), raw[k].ravel())
 
 
+def test_load_network_cache(W, tmp_path, monkeypatch):
+    """load_network parses once, then serves the same arrays from the cache
+    keyed by the file's hash; a changed file gets its own entry."""
+    import os
+    raw = W.synthetic_raw_network(1, 8, 14)
+    path, cache = str(tmp_path / "net.txt.gz"), str(tmp_path / "cache")
+    W.write_v1(raw, path)
+    first = W.load_network(path, cache)
+    assert len(os.listdir(cache)) == 1 and first["U"] == [None] * 3
+    want = W.prepare(raw)
+
+    def no_parse(_):
+        raise AssertionError("parsed again although cached")
+    monkeypatch.setattr(W, "read_v1", no_parse)
+    second = W.load_network(path, cache)
+    for net in (first, second):
+        for l in range(3):
+            assert np.array_equal(net["filters"][l], raw["conv_w"][l])
+            assert np.array_equal(net["bn_mean"][l], want["bn_mean"][l])
+            assert np.array_equal(net["bn_invstd"][l], want["bn_invstd"][l])
+        for k, v in want["heads"].items():
+            assert np.array_equal(net["heads"][k], v)
+    monkeypatch.undo()
+    raw["bn_mean"][0] = raw["bn_mean"][0] + 1
+    W.write_v1(raw, path)
+    third = W.load_network(path, cache)
+    assert len(os.listdir(cache)) == 2
+    assert np.array_equal(third["bn_mean"][0], want["bn_mean"][0] + 1)
+
+
 def test_v1_file_rejects_bad_files(W, tmp_path):
     raw = W.synthetic_raw_network(1, 8, 13)
     path = str(tmp_path / "net.txt")
