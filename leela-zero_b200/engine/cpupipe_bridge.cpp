@@ -23,6 +23,8 @@ std::vector<int> gpus{0};
 CUDAPipe::Precision precision = CUDAPipe::Precision::FP16;
 std::atomic<unsigned long long> evals{0};
 CUDAPipe* last_pipe = nullptr;
+int callers = 0;     // threads that will call forward(); 0: cfg_num_threads
+bool eager = false;  // CUDAPipe::Batching::EAGER instead of the reference's wait rule
 }  // namespace lzb_engine
 
 namespace {
@@ -38,8 +40,11 @@ CUDAPipe* pipe_of(const CPUPipe* self) {
 void CPUPipe::initialize(const int channels) {
     m_input_channels = channels;
     std::unique_ptr<CUDAPipe> pipe(new CUDAPipe(lzb_engine::gpus, static_cast<int>(cfg_batch_size),
-                                                static_cast<int>(cfg_num_threads),
+                                                lzb_engine::callers > 0
+                                                    ? lzb_engine::callers
+                                                    : static_cast<int>(cfg_num_threads),
                                                 lzb_engine::precision));
+    if (lzb_engine::eager) pipe->set_batching(CUDAPipe::Batching::EAGER);
     pipe->initialize(channels);
     std::lock_guard<std::mutex> lk(g_mutex);
     lzb_engine::last_pipe = pipe.get();

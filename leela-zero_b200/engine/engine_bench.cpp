@@ -4,14 +4,28 @@
 // and its --benchmark settings (src/Leela.cpp:467-479); moves are requested
 // through GTP::execute("genmove ...") (src/GTP.cpp:623-690).
 //
+//
+// With --games N (N > 1) it plays N games at once in this one process: every
+// game has its own GameState and UCTSearch (src/UCTSearch.h:113-114) with
+// --threads search threads, all games share one Network and therefore one
+// CUDAPipe queue, so that batches form across games (N x T callers) instead of
+// inside one tree.  Self-play settings as autogtp uses them (root noise, moves
+// drawn in proportion to visits for the first 30 moves) keep the games apart.
+// The engine has one process-wide piece of state a search writes to, the
+// training record (src/UCTSearch.cpp:847, src/Training.h:103); its call is
+// serialised at link time (training_lock.cpp), the engine's sources stay as
+// they are.
+//
 //   engine_bench --weights FILE [--threads T] [--batch B] [--gpus G] [--visits V]
-//                [--moves M] [--precision fp16|bf16|fp32] [--verbose]
+//                [--moves M] [--games N] [--batching wait|eager]
+//                [--precision fp16|bf16|fp32] [--verbose]
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <iostream>
 #include <memory>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "config.h"
@@ -31,11 +45,43 @@ extern std::vector<int> gpus;
 extern CUDAPipe::Precision precision;
 extern std::atomic<unsigned long long> evals;
 extern CUDAPipe* last_pipe;
+extern int callers;
+extern bool eager;
 }  // namespace lzb_engine
+
+namespace {
+// N games at once on one shared network; returns the number of moves played.
+int play_games(Network& network, int games, int moves) {
+    std::vector<std::unique_ptr<GameState>> states;
+    std::vector<std::unique_ptr<UCTSearch>> searches;
+    for (int g = 0; g < games; g++) {
+        states.emplace_back(new GameState());
+        states.back()->init_game(BOARD_SIZE, KOMI);
+        states.back()->set_timecontrol(0, 1, 0, 0);
+        searches.emplace_back(new UCTSearch(*states.back(), network));
+    }
+    std::atomic<int> played{0};
+    std::vector<std::thread> players;
+    for (int g = 0; g < games; g++) {
+        players.emplace_back([&, g] {
+            Random::get_Rng().seedrandom(cfg_rng_seed + 1000 * (g + 1));
+            GameState& game = *states[g];
+            for (int m = 0; m < moves && game.get_passes() < 2; m++) {
+                const int color = game.get_to_move();
+                const int move = searches[g]->think(color);
+                game.play_move(color, move);
+                played++;
+            }
+        });
+    }
+    for (auto& t : players) t.join();
+    return played.load();
+}
+}  // namespace
 
 int main(int argc, char** argv) {
     std::string weights;
-    int threads = 8, batch = 8, ngpus = 1, visits = 1600, moves = 50;
+    int threads = 8, batch = 8, ngpus = 1, visits = 1600, moves = 50, games = 1;
     bool verbose = false;
     for (int i = 1; i < argc; i++) {
         const std::string k = argv[i];
@@ -48,6 +94,8 @@ int main(int argc, char** argv) {
         else if (k == "--gpus") ngpus = std::atoi(v.c_str());
         else if (k == "--visits") visits = std::atoi(v.c_str());
         else if (k == "--moves") moves = std::atoi(v.c_str());
+        else if (k == "--games") games = std::atoi(v.c_str());
+        else if (k == "--batching") lzb_engine::eager = (v == "eager");
         else if (k == "--precision") {
             lzb_engine::precision = v == "fp32" ? CUDAPipe::Precision::FP32
                                   : v == "bf16" ? CUDAPipe::Precision::BF16 : CUDAPipe::Precision::FP16;
@@ -70,39 +118,51 @@ int main(int argc, char** argv) {
     cfg_resignpct = 0;
     cfg_quiet = !verbose;
     cfg_weightsfile = weights;
+    if (games < 1 || threads < 1) { std::fprintf(stderr, "bad --games/--threads\n"); return 2; }
+    if (games > 1) {
+        cfg_noise = true;          // autogtp's self-play options: -n, -m 30
+        cfg_random_cnt = 30;
+        lzb_engine::callers = games * threads;
+    }
 
     setbuf(stdout, nullptr);
-    thread_pool.initialize(cfg_num_threads);
+    thread_pool.initialize(static_cast<size_t>(cfg_num_threads) * games);
     auto rng = std::make_unique<Random>(5489);
     Zobrist::init_zobrist(*rng);
     Random::get_Rng().seedrandom(cfg_rng_seed);
     Utils::create_z_table();
+    auto network = std::make_unique<Network>();
     {
-        auto network = std::make_unique<Network>();
-        const auto playouts = std::min(cfg_max_playouts, cfg_max_visits);
+        // the cache is sized from the playout limit (src/Network.cpp:578-587); N games share it
+        const auto playouts = std::min(cfg_max_playouts, cfg_max_visits) * games;
         network->initialize(playouts, cfg_weightsfile);
-        GTP::initialize(std::move(network));
     }
-
     auto game = std::make_unique<GameState>();
-    game->init_game(BOARD_SIZE, KOMI);
-    game->set_timecontrol(0, 1, 0, 0);   // infinite time, as --benchmark does
+    if (games == 1) {
+        GTP::initialize(std::move(network));
+        game->init_game(BOARD_SIZE, KOMI);
+        game->set_timecontrol(0, 1, 0, 0);   // infinite time, as --benchmark does
+    }
 
     const auto evals0 = lzb_engine::evals.load();
     const auto t0 = std::chrono::steady_clock::now();
     int played = 0;
-    for (int m = 0; m < moves; m++) {
-        GTP::execute(*game, (m % 2 == 0) ? "genmove b" : "genmove w");
-        played++;
-        if (game->get_passes() >= 2) break;
+    if (games > 1) {
+        played = play_games(*network, games, moves);
+    } else {
+        for (int m = 0; m < moves; m++) {
+            GTP::execute(*game, (m % 2 == 0) ? "genmove b" : "genmove w");
+            played++;
+            if (game->get_passes() >= 2) break;
+        }
     }
     const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     const auto evals = lzb_engine::evals.load() - evals0;
     const auto s = lzb_engine::last_pipe ? lzb_engine::last_pipe->stats() : CUDAPipe::Stats();
-    std::printf("\n{\"moves\": %d, \"seconds\": %.3f, \"visits_per_move\": %d, \"threads\": %d, "
-                "\"batch\": %d, \"gpus\": %d, \"nn_evals\": %llu, \"nn_evals_per_s\": %.1f, "
+    std::printf("\n{\"games\": %d, \"moves\": %d, \"seconds\": %.3f, \"visits_per_move\": %d, \"threads\": %d, "
+                "\"batch\": %d, \"batching\": \"%s\", \"gpus\": %d, \"nn_evals\": %llu, \"nn_evals_per_s\": %.1f, "
                 "\"visits_per_s\": %.1f, \"batches\": %zu, \"mean_batch\": %.2f, \"timeouts\": %zu}\n",
-                played, sec, visits, threads, batch, ngpus, evals, evals / sec,
+                games, played, sec, visits, threads, batch, lzb_engine::eager ? "eager" : "wait", ngpus, evals, evals / sec,
                 double(played) * visits / sec, s.batches,
                 s.batches ? double(s.positions) / s.batches : 0.0, s.timeouts);
     return 0;

@@ -3,6 +3,7 @@ network and report NN evaluations/s, visits/s and the engine's own playouts/s.
 
     python leela-zero_b200/engine/run_engine.py --blocks 15 --filters 192 \
         --threads 8 --batch 8 --gpus 1 --visits 1600 --moves 50
+    python leela-zero_b200/engine/run_engine.py --games 16 --threads 8 --batch 128 --moves 30
 
 The binary is built by the Makefile beside this file from the engine's own
 sources (only where the reference tree is present; the built binary is used
@@ -38,7 +39,7 @@ def write_network(blocks, filters, seed, path):
 
 
 def run(blocks, filters, threads, batch, gpus, visits, moves, precision="fp16", seed=2004,
-        weights=None, verbose=True, timeout=3600):
+        weights=None, verbose=True, timeout=3600, games=1, batching="wait"):
     if not os.path.exists(EXE):
         raise RuntimeError("%s is missing: make -C %s (needs the reference tree)" % (EXE, HERE))
     tmp = None
@@ -48,8 +49,9 @@ def run(blocks, filters, threads, batch, gpus, visits, moves, precision="fp16", 
         weights = tmp.name
         write_network(blocks, filters, seed, weights)
     cmd = [EXE, "--weights", weights, "--threads", str(threads), "--batch", str(batch), "--gpus",
-           str(gpus), "--visits", str(visits), "--moves", str(moves), "--precision", precision]
-    if verbose:
+           str(gpus), "--visits", str(visits), "--moves", str(moves), "--precision", precision,
+           "--games", str(games), "--batching", batching]
+    if verbose and games == 1:
         cmd.append("--verbose")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
     if tmp is not None:
@@ -75,8 +77,12 @@ if __name__ == "__main__":
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--visits", type=int, default=1600)
     ap.add_argument("--moves", type=int, default=50)
+    ap.add_argument("--games", type=int, default=1,
+                    help="games played at once in one process, sharing the pipe's queue")
+    ap.add_argument("--batching", default="wait", choices=("wait", "eager"),
+                    help="wait: the reference's full-batch-or-timeout rule; eager: take what is waiting")
     ap.add_argument("--precision", default="fp16")
     ap.add_argument("--weights", default=None)
     a = ap.parse_args()
     print(json.dumps(run(a.blocks, a.filters, a.threads, a.batch, a.gpus, a.visits, a.moves,
-                         a.precision, weights=a.weights)))
+                         a.precision, weights=a.weights, games=a.games, batching=a.batching)))

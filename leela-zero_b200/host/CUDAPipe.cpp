@@ -123,10 +123,13 @@ void CUDAPipe::push_weights(unsigned int /*filter_size*/, unsigned int /*channel
     // Same sizing rule as the reference: at least one worker per GPU, more when
     // many search threads share few GPUs (src/OpenCLScheduler.cpp:113-114).
     m_workers_per_gpu = m_num_threads / m_batch_size / (static_cast<int>(m_gpus.size()) + 1) + 1;
+    // EAGER keeps two batches per GPU in flight (one computing, one being staged)
+    if (m_batching == Batching::EAGER && m_workers_per_gpu < 2) m_workers_per_gpu = 2;
     m_backend->load(m_gpus, m_channels, blocks, m_batch_size, m_workers_per_gpu, m_precision,
                     *weights);
     m_live_gpus = static_cast<int>(m_gpus.size());
     m_gpu_failed.assign(m_gpus.size(), 0);
+    m_in_flight.assign(m_gpus.size(), 0);
     for (size_t g = 0; g < m_gpus.size(); g++) {
         for (int s = 0; s < m_workers_per_gpu; s++) {
             m_threads.emplace_back(&CUDAPipe::worker, this, static_cast<int>(g), s);
@@ -171,11 +174,39 @@ void CUDAPipe::forward(const std::vector<float>& input, std::vector<float>& outp
 // Batch-forming heuristic of the reference (src/OpenCLScheduler.cpp:293-353):
 // wait up to m_wait_ms for a full batch; if it does not fill and no other
 // partial batch is in flight, send what is there and wait 1 ms less next time.
-std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out) {
+//
+// Batching::EAGER instead: take what is waiting as soon as there is room for
+// another batch on the worker's GPU (two per GPU), after a gathering window in which the
+// callers released together by the previous batch come back.
+std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out, int gpu_index) {
     std::vector<EntryPtr> batch;
     *timed_out = false;
     std::unique_lock<std::mutex> lk(m_mutex);
     size_t count = 0;
+    const size_t full = static_cast<size_t>(m_batch_size);
+    while (m_batching == Batching::EAGER) {
+        m_cv.wait(lk, [&] {
+            return !m_running || (!m_queue.empty() && !m_gathering &&
+                                  (m_queue.size() >= full || m_in_flight[gpu_index] < 2));
+        });
+        if (!m_running) return batch;
+        if (m_queue.size() < full && m_gather_us > 0) {
+            m_gathering = true;
+            m_cv.wait_for(lk, std::chrono::microseconds(m_gather_us),
+                          [&] { return !m_running || m_queue.size() >= full; });
+            m_gathering = false;
+            if (!m_running) return batch;
+        }
+        count = std::min(m_queue.size(), full);
+        if (count == 0) continue;          // drained while gathering
+        *timed_out = count < full;
+        m_in_flight[gpu_index]++;
+        batch.assign(m_queue.begin(), m_queue.begin() + count);
+        m_queue.erase(m_queue.begin(), m_queue.begin() + count);
+        lk.unlock();
+        m_cv.notify_all();                 // others may take what is left
+        return batch;
+    }
     while (true) {
         if (!m_running) return batch;
         count = m_queue.size();
@@ -218,7 +249,7 @@ void CUDAPipe::worker(int gpu_index, int slot) {
             if (m_gpu_failed[gpu_index]) return;   // a sibling worker saw this GPU fail
         }
         bool timed_out = false;
-        auto batch = pickup(&timed_out);
+        auto batch = pickup(&timed_out, gpu_index);
         if (batch.empty()) return;   // shutting down
         const int n = static_cast<int>(batch.size());
         for (int i = 0; i < n; i++) {
@@ -243,9 +274,11 @@ void CUDAPipe::worker(int gpu_index, int slot) {
             m_stats.positions += n;
             if (n == m_batch_size) m_stats.full_batches++;
             if (timed_out) m_stats.timeouts++;
+            if (m_batching == Batching::EAGER) m_in_flight[gpu_index]--;
         }
         for (auto& e : batch) finish(e, false, rc == 0 ? std::string() : error);
-        if (timed_out) m_partial_in_progress = false;
+        if (m_batching == Batching::EAGER) m_cv.notify_all();   // room for another batch
+        else if (timed_out) m_partial_in_progress = false;
         if (rc != 0) {
             // This GPU leaves the rotation (its other workers stop at their
             // next turn).  If it was the last one, wake everybody who waits.
@@ -264,6 +297,13 @@ void CUDAPipe::worker(int gpu_index, int slot) {
             return;
         }
     }
+}
+
+void CUDAPipe::set_batching(Batching mode, int gather_us) {
+    std::lock_guard<std::mutex> lk(m_mutex);
+    if (!m_threads.empty()) throw std::runtime_error("CUDAPipe: set_batching after push_weights");
+    m_batching = mode;
+    m_gather_us = gather_us < 0 ? 0 : gather_us;
 }
 
 void CUDAPipe::drain() {

@@ -17,7 +17,13 @@
 //    that batch get std::runtime_error, the other GPUs keep serving;
 //  * the adaptive wait for a full batch is capped at 100 ms (the reference lets it
 //    grow by 2 ms per arriving request without bound);
-//  * nothing here calls exit().
+//  * nothing here calls exit();
+//  * a second batch-forming rule, Batching::EAGER, for callers that do not come
+//    from one search tree (many games in one process): a worker takes whatever
+//    is waiting as soon as its GPU has room for another batch, after a short
+//    gathering window, instead of waiting for a full batch.  Batch sizes then
+//    follow the arrival rate: small while the GPU keeps up, full when it is the
+//    limit.  The reference's rule stays the default.
 #ifndef LZB_CUDAPIPE_H
 #define LZB_CUDAPIPE_H
 
@@ -61,6 +67,9 @@ public:
         virtual void free_staging(float* p) { delete[] p; }
     };
 
+    // How a worker decides that a batch is ready (see the header comment).
+    enum class Batching { REFERENCE_WAIT = 0, EAGER = 1 };
+
     struct Stats {
         std::size_t batches = 0;        // backend calls
         std::size_t positions = 0;      // positions evaluated
@@ -87,6 +96,9 @@ public:
 
     Stats stats() const;
     int live_gpus() const;
+    // Call before push_weights.  gather_us: how long an EAGER worker lets
+    // further requests join once the first one is there.
+    void set_batching(Batching mode, int gather_us = 100);
 
     static constexpr int kInputFloats = 18 * 361;
     static constexpr int kPolicyFloats = 2 * 361;
@@ -109,7 +121,7 @@ private:
     using EntryPtr = std::shared_ptr<Entry>;
 
     void worker(int gpu_index, int slot);
-    std::vector<EntryPtr> pickup(bool* timed_out);
+    std::vector<EntryPtr> pickup(bool* timed_out, int gpu_index);
     static void finish(const EntryPtr& e, bool halted, const std::string& error);
 
     std::vector<int> m_gpus;
@@ -127,6 +139,10 @@ private:
     std::atomic<bool> m_draining{false};
     std::atomic<bool> m_partial_in_progress{false};
     int m_wait_ms = 10;                 // start with 10 ms, adapted like the reference
+    Batching m_batching = Batching::REFERENCE_WAIT;
+    int m_gather_us = 100;
+    std::vector<int> m_in_flight;       // EAGER: per GPU, batches picked up and not yet finished
+    bool m_gathering = false;           // EAGER: a worker is inside its gathering window
     std::atomic<int> m_live_gpus{0};
     std::vector<char> m_gpu_failed;     // per GPU, guarded by m_mutex
     std::vector<std::thread> m_threads;

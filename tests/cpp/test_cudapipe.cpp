@@ -35,6 +35,8 @@ public:
     std::atomic<int> fail_gpu{-1};       // gpu index whose calls fail
     std::atomic<int> delay_ms{0};
     std::atomic<bool> gate_closed{false};  // while true, forward() blocks
+    std::atomic<int> running[4] = {{0}, {0}, {0}, {0}};   // calls inside forward(), per gpu
+    std::atomic<int> max_running{0};
     std::mutex m;
     std::multiset<int> batch_sizes;
     std::set<int> gpus_used;
@@ -48,6 +50,15 @@ public:
     int forward(int gpu, int, const float* in, int n, float* pol, float* val,
                 std::string* error) override {
         calls++;
+        struct Count {
+            std::atomic<int>& c;
+            explicit Count(std::atomic<int>& x, std::atomic<int>& mx) : c(x) {
+                const int now = ++c;
+                int prev = mx.load();
+                while (now > prev && !mx.compare_exchange_weak(prev, now)) {}
+            }
+            ~Count() { --c; }
+        } count(running[gpu & 3], max_running);
         while (gate_closed) std::this_thread::sleep_for(std::chrono::milliseconds(1));
         if (delay_ms > 0) std::this_thread::sleep_for(std::chrono::milliseconds(delay_ms));
         {
@@ -95,10 +106,12 @@ struct Caller {
     }
 };
 
-static std::unique_ptr<CUDAPipe> make_pipe(FakeBackend** fb, std::vector<int> gpus, int batch, int threads) {
+static std::unique_ptr<CUDAPipe> make_pipe(FakeBackend** fb, std::vector<int> gpus, int batch, int threads,
+                                           bool eager = false) {
     auto backend = std::unique_ptr<FakeBackend>(new FakeBackend);
     *fb = backend.get();
     std::unique_ptr<CUDAPipe> pipe(new CUDAPipe(std::move(gpus), batch, threads, CUDAPipe::Precision::FP16, std::move(backend)));
+    if (eager) pipe->set_batching(CUDAPipe::Batching::EAGER, 100);
     pipe->initialize(8);
     pipe->push_weights(6, 18, 8, tiny_weights());
     return pipe;
@@ -263,6 +276,90 @@ static void test_destructor_releases_waiters() {
     CHECK(released == 3);
 }
 
+// Batching::EAGER: as many callers as a batch holds, so full batches hardly
+// ever form by themselves.  Batches must go as soon as the GPU has room, grow
+// while it is busy, stay within batch_size and within two calls per GPU.
+static void test_eager_batches_follow_the_load() {
+    FakeBackend* fb;
+    auto pipe = make_pipe(&fb, {0, 1}, 64, 64, true);
+    fb->delay_ms = 2;
+    std::atomic<int> good{0};
+    std::vector<std::thread> ts;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int t = 0; t < 64; t++) {
+        ts.emplace_back([&, t] {
+            for (int r = 0; r < 25; r++) {
+                Caller c(t * 100.0f + r);
+                pipe->forward(c.in, c.pol, c.val);
+                if (c.answer_is_mine()) good++;
+            }
+        });
+    }
+    for (auto& t : ts) t.join();
+    const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    auto s = pipe->stats();
+    CHECK(good == 64 * 25 && s.positions == 64 * 25);
+    CHECK(fb->max_n <= 64);
+    CHECK(fb->max_running <= 2);                              // per GPU: one computing, one staged
+    CHECK(double(s.positions) / s.batches >= 4.0);            // requests gathered while the GPUs were busy
+    CHECK(sec < 1.5);                                         // 25 rounds of 2 ms calls, not 25 waits of 10 ms
+    CHECK(fb->gpus_used.size() == 2);
+    std::printf("eager: %zu batches for %zu positions (mean %.1f), %.3f s\n", s.batches, s.positions,
+                double(s.positions) / s.batches, sec);
+}
+
+static void test_eager_single_caller_is_served_at_once() {
+    FakeBackend* fb;
+    auto pipe = make_pipe(&fb, {0}, 16, 16, true);
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int r = 0; r < 20; r++) {
+        Caller c(r);
+        pipe->forward(c.in, c.pol, c.val);
+        CHECK(c.answer_is_mine());
+    }
+    const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    CHECK(pipe->stats().batches == 20);
+    CHECK(sec < 0.1);                                         // 20 gathering windows of 100 us, no 10 ms waits
+}
+
+static void test_eager_drain_failure_and_shutdown() {
+    FakeBackend* fb;
+    auto pipe = make_pipe(&fb, {0, 1}, 4, 8, true);
+    fb->gate_closed = true;
+    std::atomic<int> halted{0}, answered{0}, failed{0};
+    std::vector<std::thread> ts;
+    for (int t = 0; t < 24; t++) {
+        ts.emplace_back([&, t] {
+            Caller c(t);
+            try {
+                pipe->forward(c.in, c.pol, c.val);
+                if (c.answer_is_mine()) answered++;
+            } catch (const NetworkHaltException&) {
+                halted++;
+            }
+        });
+    }
+    std::this_thread::sleep_for(std::chrono::milliseconds(100));
+    pipe->drain();                                // 2 GPUs x 2 calls x 4 positions are in the backend, 8 wait
+    std::this_thread::sleep_for(std::chrono::milliseconds(50));
+    CHECK(halted >= 8);
+    fb->gate_closed = false;
+    for (auto& t : ts) t.join();
+    CHECK(halted + answered == 24 && answered >= 4);
+    pipe->resume();
+    fb->fail_gpu = 1;
+    for (int r = 0; r < 30; r++) {
+        Caller c(r);
+        try { pipe->forward(c.in, c.pol, c.val); CHECK(c.answer_is_mine()); }
+        catch (const std::runtime_error&) { failed++; }
+    }
+    CHECK(failed >= 1 && failed <= 2 && pipe->live_gpus() == 1);
+    bool threw = false;
+    try { pipe->set_batching(CUDAPipe::Batching::REFERENCE_WAIT); } catch (const std::runtime_error&) { threw = true; }
+    CHECK(threw);                                 // the rule is fixed once the workers run
+    pipe.reset();                                 // workers idle in the eager wait must leave
+}
+
 int main() {
     test_many_callers_two_gpus();
     test_single_caller_does_not_deadlock();
@@ -271,6 +368,9 @@ int main() {
     test_failing_gpu_is_removed();
     test_bad_arguments();
     test_destructor_releases_waiters();
+    test_eager_batches_follow_the_load();
+    test_eager_single_caller_is_served_at_once();
+    test_eager_drain_failure_and_shutdown();
     if (g_failures == 0) std::printf("ALL OK\n");
     return g_failures == 0 ? 0 : 1;
 }

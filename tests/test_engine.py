@@ -78,3 +78,18 @@ def test_engine_plays_on_cudapipe():
     assert out["nn_evals"] >= 8 * 50                          # at least half the visits needed a fresh evaluation
     assert out["batches"] < out["nn_evals"]                   # requests were batched
     assert out.get("engine_playouts", 0) > 0                  # the engine's own statistics line was seen
+
+
+@pytest.mark.gpu
+def test_concurrent_games_share_the_queue():
+    """Six games at once, two search threads each, one network: all games
+    finish their moves and the batches are larger than one tree's two callers
+    could make them."""
+    run_engine = _runner()
+    if not os.path.exists(run_engine.EXE):
+        pytest.skip("engine_bench not built (needs the reference tree)")
+    out = run_engine.run(blocks=2, filters=32, threads=2, batch=12, gpus=1, visits=60, moves=6,
+                         precision="fp16", seed=2081, games=6, batching="eager")
+    assert out["games"] == 6 and out["moves"] == 36
+    assert out["nn_evals"] >= 36 * 20
+    assert out["mean_batch"] > 2.0
