@@ -24,7 +24,7 @@ CUDAPipe::Precision precision = CUDAPipe::Precision::FP16;
 std::atomic<unsigned long long> evals{0};
 CUDAPipe* last_pipe = nullptr;
 int callers = 0;     // threads that will call forward(); 0: cfg_num_threads
-bool eager = false;  // CUDAPipe::Batching::EAGER instead of the reference's wait rule
+bool eager = true;   // CUDAPipe::Batching::EAGER (measured faster under the engine); false: the reference's wait rule
 }  // namespace lzb_engine
 
 namespace {

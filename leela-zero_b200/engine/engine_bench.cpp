@@ -17,7 +17,7 @@
 // they are.
 //
 //   engine_bench --weights FILE [--threads T] [--batch B] [--gpus G] [--visits V]
-//                [--moves M] [--games N] [--batching wait|eager]
+//                [--moves M] [--games N] [--batching eager|wait]
 //                [--precision fp16|bf16|fp32] [--verbose]
 #include <chrono>
 #include <cstdio>

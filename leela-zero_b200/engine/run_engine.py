@@ -39,7 +39,7 @@ def write_network(blocks, filters, seed, path):
 
 
 def run(blocks, filters, threads, batch, gpus, visits, moves, precision="fp16", seed=2004,
-        weights=None, verbose=True, timeout=3600, games=1, batching="wait"):
+        weights=None, verbose=True, timeout=3600, games=1, batching="eager"):
     if not os.path.exists(EXE):
         raise RuntimeError("%s is missing: make -C %s (needs the reference tree)" % (EXE, HERE))
     tmp = None
@@ -79,7 +79,7 @@ if __name__ == "__main__":
     ap.add_argument("--moves", type=int, default=50)
     ap.add_argument("--games", type=int, default=1,
                     help="games played at once in one process, sharing the pipe's queue")
-    ap.add_argument("--batching", default="wait", choices=("wait", "eager"),
+    ap.add_argument("--batching", default="eager", choices=("eager", "wait"),
                     help="wait: the reference's full-batch-or-timeout rule; eager: take what is waiting")
     ap.add_argument("--precision", default="fp16")
     ap.add_argument("--weights", default=None)
