@@ -194,6 +194,22 @@ def run_reference(args):
     }))
 
 
+def default_micro_batch(precision, B):
+    """Positions per pass through the tower as the library chooses them: the
+    whole batch for the direct convolution, 64 in fp32, and in the 16-bit
+    Winograd modes the first count from 64 up for which the transform kernel's
+    grid (FILTERS / 64 x positions) is whole waves of the SMs."""
+    if precision in ("fp16", "bf16"):
+        return B
+    n = 64
+    if precision != "fp32":
+        import torch
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        groups = -(-FILTERS // 64)
+        n = next((c for c in range(64, min(2 * sms, 256) + 1) if (groups * c) % sms == 0), 64)
+    return min(n, B)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -314,9 +330,11 @@ def main():
         e2e = whole_job_rate(B, world, ms_e2e)
         g_ms, g_n = prof["contraction"]
         winograd = args.precision != "fp16" and args.precision != "bf16"
-        micro = args.micro_batch or (min(64, B) if winograd else B)
-        # every contraction launch but the input layer's covers one micro-batch of one tower layer
-        flops_per_launch = (FLOPS_GEMM_PER_POS if winograd else FLOPS_CONV_PER_POS) * micro
+        micro = args.micro_batch or default_micro_batch(args.precision, B)
+        # every contraction launch but the input layer's covers one micro-batch of one tower
+        # layer; the last micro-batch of a step may be shorter, so take the mean size
+        passes = -(-B // micro)
+        flops_per_launch = (FLOPS_GEMM_PER_POS if winograd else FLOPS_CONV_PER_POS) * B / passes
         avg_s = (g_ms / max(g_n, 1)) * 1e-3
         achieved = flops_per_launch / avg_s / 1e12 if avg_s > 0 else 0.0
         peak = peaks["bf16_tflops_sustained"]
@@ -355,7 +373,7 @@ def main():
             cores = os.cpu_count() or 1
             sys.path.insert(0, os.path.join(ROOT, "oracle"))
             import oracle as O
-            npos = 2 * cores if O.ref_available() else 2
+            npos = 8 * cores if O.ref_available() else 4    # a few seconds on every core
             rate, kind, threads, dt = cpu_reference_rate(net, W, npos, cores)
             out["cpu_baseline"] = {"value": rate, "unit": "positions/s", "cores": threads, "kind": kind,
                                    "sample": "%d positions of the same network, %d threads, %.1f s"

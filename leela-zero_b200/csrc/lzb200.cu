@@ -854,6 +854,24 @@ int lzb_pipe_finalize(lzb_pipe* p) {
     return LZB_OK;
 }
 
+// Positions per pass through the tower.  Direct convolution: the whole batch.
+// Winograd pipeline: V and M of one micro-batch should stay in L2 (64 positions
+// x 256 channels = 2 x 29 MB in 16 bits); in the 16-bit modes the fused
+// transform runs one CTA per SM (25 warps), so the count is raised to the next
+// one that makes its grid, (channels / 64) x positions, whole waves of the SMs
+// (74 for 256 channels on 148 SMs: +10 % measured against 64).
+static int default_micro_batch(const lzb_pipe* p, int cap) {
+    if (p->direct) return cap;
+    int n = kDefaultMicroBatch;
+    if (p->elt == 2) {
+        const int groups = p->Cp / kChanPerCta;
+        for (int cand = kDefaultMicroBatch; cand <= 2 * p->sm_count && cand <= kMaxMicroBatch; cand++) {
+            if ((groups * cand) % p->sm_count == 0) { n = cand; break; }
+        }
+    }
+    return n < cap ? n : cap;
+}
+
 int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
     if (!out) return fail(LZB_ERR_ARG, "null out");
     *out = nullptr;
@@ -878,7 +896,7 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
         alloc(&c->X, (size_t)c->Qa * p->Cp * p->elt);
         alloc(&c->H, (size_t)c->Qa * p->Cp * p->elt);
     } else {
-        c->micro = c->micro_cap < kDefaultMicroBatch ? c->micro_cap : kDefaultMicroBatch;
+        c->micro = default_micro_batch(p, c->micro_cap);
         c->Pa = round_up(c->micro_cap * kTilesPerPos, 128);
         const size_t vm = (size_t)kPoints * c->Pa * p->Cp * p->elt;
         alloc(&c->V, vm);
@@ -940,7 +958,7 @@ void lzb_ctx_destroy(lzb_ctx* c) {
 
 int lzb_ctx_set_micro_batch(lzb_ctx* c, int positions) {
     if (!c) return fail(LZB_ERR_ARG, "null context");
-    if (positions == 0) positions = c->pipe->direct ? c->micro_cap : kDefaultMicroBatch;
+    if (positions == 0) positions = default_micro_batch(c->pipe, c->micro_cap);
     if (positions < 1) return fail(LZB_ERR_ARG, "bad micro-batch");
     c->micro = positions < c->micro_cap ? positions : c->micro_cap;
     return LZB_OK;
