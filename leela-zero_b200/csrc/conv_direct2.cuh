@@ -32,6 +32,15 @@ constexpr int kPairM = 2 * kTileM;                         // 256 cells per CTA 
 constexpr int kB2Stages = 10;                              // ring of half weight tiles
 constexpr uint32_t kB2StageBytes = (kMaxN / 2) * 128;      // 16 KB
 constexpr uint32_t kOperand2Bytes = kWinBufs * kWinBytes + kB2Stages * kB2StageBytes;
+// The same shared memory cut differently when the output channels are sliced
+// (small batches, a chain of short launches bound by load latency): all four
+// activation windows of a unit in flight at once and fewer, fuller weight
+// stages, each carrying the slices of up to three taps.
+constexpr int kWinBufsSliced = 4;
+constexpr int kB2StagesSliced = 7;
+constexpr int kMaxTapsPerStage = 3;
+static_assert(kWinBufsSliced * kWinBytes + kB2StagesSliced * kB2StageBytes <= kOperand2Bytes,
+              "the sliced layout must fit the operand area");
 constexpr uint32_t kD2SmemBytes =
     kOperand2Bytes + 8 * kStageOutBytes + 2 * kMaxN * 4 + kBarBytes + 1024;
 
@@ -92,7 +101,8 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
 }
 
 // tmX : activations [Qa][Cin], box 64 x kWinRows.
-// tmW : weights [9*Kp][Cin], box 64 x Kp/(2*nsplit).
+// tmW : weights [9*Kp][Cin], box 64 x Kp/(2*nsplit) (one tap's rows of one CTA's
+//       half slice; a stage of the ring takes up to three such boxes when sliced).
 // tmO : outputs [Qa][Kp], box 32 x 32, 64-byte swizzle.
 // npairs : 256-cell tiles covering Q.  nsplit : the output channels of a tile are
 // cut into nsplit slices of N = Kp/nsplit (a multiple of 64), each slice a work
@@ -114,8 +124,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (base - raw);
+    const bool sliced = nsplit > 1;
+    const int nwin = sliced ? kWinBufsSliced : kWinBufs;
+    const int nstages = sliced ? kB2StagesSliced : kB2Stages;
     const uint32_t win_base = base;
-    const uint32_t b_base = base + kWinBufs * kWinBytes;
+    const uint32_t b_base = base + static_cast<uint32_t>(nwin) * kWinBytes;
     unsigned char* stage_out = smem + kOperand2Bytes;
     float* s_scale = reinterpret_cast<float*>(stage_out + 8 * kStageOutBytes);
     float* s_bias = s_scale + kMaxN;
@@ -124,11 +137,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     auto bfull_bar = [&](int s) { return bars + 8u * (0 + s); };      // leader's are used
     auto bempty_bar = [&](int s) { return bars + 8u * (16 + s); };    // both CTAs
     auto wfull_bar = [&](int w) { return bars + 8u * (32 + w); };     // leader's
-    auto wempty_bar = [&](int w) { return bars + 8u * (34 + w); };    // both
-    auto tfull_bar = [&](int a) { return bars + 8u * (36 + a); };     // both
-    auto tempty_bar = [&](int a) { return bars + 8u * (38 + a); };    // leader's
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * 40);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 40 + 8);
+    auto wempty_bar = [&](int w) { return bars + 8u * (36 + w); };    // both
+    auto tfull_bar = [&](int a) { return bars + 8u * (40 + a); };     // both
+    auto tempty_bar = [&](int a) { return bars + 8u * (42 + a); };    // leader's
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * 44);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 44 + 8);
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -140,7 +153,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             mbar_init(bfull_bar(i), 2);      // one arrive.expect_tx per CTA of the pair
             mbar_init(bempty_bar(i), 1);
         }
-        for (int i = 0; i < kWinBufs; i++) {
+        for (int i = 0; i < kWinBufsSliced; i++) {
             mbar_init(wfull_bar(i), 2);
             mbar_init(wempty_bar(i), 1);
         }
@@ -175,6 +188,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     const int unit_end = static_cast<int>(static_cast<long long>(cid + 1) * units / nclusters);
     const int n_slice = Kp / nsplit;          // MMA N
     const int half_n = n_slice >> 1;          // weight rows each CTA stages
+    // taps whose weight slices share one stage of the ring (1 for whole tiles)
+    const int taps_per_stage =
+        sliced ? ((kMaxN / 2) / half_n < kMaxTapsPerStage ? (kMaxN / 2) / half_n : kMaxTapsPerStage) : 1;
 
     // Activations, residuals and outputs belong to the chain of kernels in the
     // stream: nobody touches them before the previous kernel has finished.
@@ -199,15 +215,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                     const uint32_t wf = map_to_cta(wfull_bar(wb), 0);
                     mbar_expect_tx_cluster(wf, kWinBytes);
                     tma_load_2d_pair(win_base + wb * kWinBytes, &tmX, c * kChunkK, m0 - kWinPad, wf);
-                    if (++wb == kWinBufs) { wb = 0; wphase ^= 1u; }
-                    for (int tap = 0; tap < 9; ++tap) {
+                    if (++wb == nwin) { wb = 0; wphase ^= 1u; }
+                    for (int tap = 0; tap < 9; tap += taps_per_stage) {
+                        const int g = 9 - tap < taps_per_stage ? 9 - tap : taps_per_stage;
                         ok = mbar_wait(bempty_bar(stage), phase ^ 1u, abort_flag, err, kErrD2Producer);
                         if (!ok) break;
                         const uint32_t bf = map_to_cta(bfull_bar(stage), 0);
-                        mbar_expect_tx_cluster(bf, btx);
-                        tma_load_2d_pair(b_base + stage * kB2StageBytes, &tmW, c * kChunkK,
-                                         tap * Kp + wrow0, bf);
-                        if (++stage == kB2Stages) { stage = 0; phase ^= 1u; }
+                        mbar_expect_tx_cluster(bf, btx * static_cast<uint32_t>(g));
+                        for (int j = 0; j < g; ++j) {
+                            tma_load_2d_pair(b_base + stage * kB2StageBytes + j * btx, &tmW,
+                                             c * kChunkK, (tap + j) * Kp + wrow0, bf);
+                        }
+                        if (++stage == nstages) { stage = 0; phase ^= 1u; }
                     }
                 }
             }
@@ -234,24 +253,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                     ok = mbar_wait(wfull_bar(wb), wphase, abort_flag, err, kErrD2MmaFull);
                     if (!ok) break;
                     const uint32_t win = win_base + wb * kWinBytes;
-                    for (int tap = 0; tap < 9; ++tap) {
+                    const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
+                    for (int tap0 = 0; tap0 < 9; tap0 += taps_per_stage) {
+                        const int g = 9 - tap0 < taps_per_stage ? 9 - tap0 : taps_per_stage;
                         ok = mbar_wait(bfull_bar(stage), phase, abort_flag, err, kErrD2MmaFull);
                         if (!ok) break;
                         tcgen05_fence_after();
-                        const int row0 = kWinPad + (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
-                        const uint64_t a_desc = umma_desc_sw128(win + static_cast<uint32_t>(row0) * 128u);
-                        const uint64_t b_desc = umma_desc_sw128(b_base + stage * kB2StageBytes);
+                        for (int j = 0; j < g; ++j) {
+                            const int tap = tap0 + j;
+                            const int row0 = kWinPad + (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
+                            const uint64_t a_desc =
+                                umma_desc_sw128(win + static_cast<uint32_t>(row0) * 128u);
+                            const uint64_t b_desc =
+                                umma_desc_sw128(b_base + stage * kB2StageBytes + j * btx);
 #pragma unroll
-                        for (int k = 0; k < kChunkK / 16; ++k) {
-                            tcgen05_mma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
-                                                 (c > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                            for (int k = 0; k < kChunkK / 16; ++k) {
+                                tcgen05_mma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                                                     (c > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                            }
                         }
                         tcgen05_commit_pair(bempty_bar(stage));
-                        if (++stage == kB2Stages) { stage = 0; phase ^= 1u; }
+                        if (++stage == nstages) { stage = 0; phase ^= 1u; }
                     }
                     if (!ok) break;
                     tcgen05_commit_pair(wempty_bar(wb));
-                    if (++wb == kWinBufs) { wb = 0; wphase ^= 1u; }
+                    if (++wb == nwin) { wb = 0; wphase ^= 1u; }
                 }
                 if (!ok) break;
                 tcgen05_commit_pair(tfull_bar(acc));
