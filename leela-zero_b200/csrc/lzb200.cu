@@ -25,6 +25,7 @@
 
 #include "conv_direct.cuh"
 #include "conv_direct2.cuh"
+#include "conv_direct3.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
 #include "head_kernels.cuh"
@@ -141,6 +142,10 @@ struct lzb_pipe {
     bool pairs = false;         // direct path on CTA pairs (tcgen05 cta_group::2)
     int elt = 2;        // bytes per stored element
     int sm_count = 0;
+    // Reduction-split kernel (conv_direct3.cuh): most tiles one launch may have
+    // (clusters of 2 * chunks CTAs that can be resident at once), per chunk
+    // count 2..4; 0 = not used.
+    int ksplit_max_tiles[5] = {0, 0, 0, 0, 0};
     std::vector<Layer> layers;
     float* head_w = nullptr;   // [3][Cp] fp32
     bool head_convs = false;
@@ -363,6 +368,36 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
     if (p->pairs) {
         const int npairs = (Q + dc2::kPairM - 1) / dc2::kPairM;
         const int max_clusters = p->sm_count / 2;
+        // Few tiles (small batches) and a tower layer: split the reduction of
+        // each tile over the pairs of one cluster.
+        const int kchunks = L.cin_p / tc::kChunkK;
+        if (kchunks >= 2 && kchunks <= dc3::kMaxSplit && p->Cp == kchunks * dc3::kGroupCols &&
+            npairs <= p->ksplit_max_tiles[kchunks]) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(npairs * 2 * kchunks);
+            cfg.blockDim = dim3(dc::kDcThreads);
+            cfg.dynamicSmemBytes = dc3::kD3SmemBytes;
+            cfg.stream = c->stream;
+            cudaLaunchAttribute attr[2];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            attr[1].id = cudaLaunchAttributeClusterDimension;
+            attr[1].val.clusterDim.x = 2 * kchunks;
+            attr[1].val.clusterDim.y = 1;
+            attr[1].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 2;
+            cudaError_t le;
+            {
+                LaunchScope scope(c, kClassContraction);
+                le = cudaLaunchKernelEx(&cfg, dc3::conv_ksplit_kernel<T>, tm_in, L.tmW2[1], tm_out, res,
+                                        (const float*)L.mean, (const float*)L.invstd, Q, p->Cp, kchunks,
+                                        c->d_err);
+            }
+            LZB_CUDA(le);
+            LZB_CUDA(cudaGetLastError());
+            return LZB_OK;
+        }
         // Small batches: cut the output channels of each tile into slices so that
         // the layer spreads over more SMs (one slice per CTA pair).
         int nsplit = 1;
@@ -492,7 +527,34 @@ int set_smem_attrs() {
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
     LZB_CUDA(cudaFuncSetAttribute(dc2::conv_direct2_kernel<__nv_bfloat16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__half>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc3::kD3SmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__nv_bfloat16>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc3::kD3SmemBytes));
     return LZB_OK;
+}
+
+// How many clusters of `csize` CTAs of the reduction-split kernel fit the
+// device at once (0 if the question fails: the kernel is then not used).
+template <typename T>
+int ksplit_resident_clusters(int csize) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(csize);
+    cfg.blockDim = dim3(dc::kDcThreads);
+    cfg.dynamicSmemBytes = dc3::kD3SmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, dc3::conv_ksplit_kernel<T>, &cfg) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
 }
 
 }  // namespace
@@ -769,6 +831,14 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     p->pairs = direct && !(getenv("LZB_CONV_PAIRS") != nullptr && atoi(getenv("LZB_CONV_PAIRS")) == 0);
     p->elt = precision == LZB_FP32 ? 4 : 2;
     p->sm_count = prop.multiProcessorCount;
+    // LZB_CONV_KSPLIT=0 keeps small batches on the sliced CTA-pair kernel
+    // (cross-check and diagnostics).
+    if (p->pairs && !(getenv("LZB_CONV_KSPLIT") != nullptr && atoi(getenv("LZB_CONV_KSPLIT")) == 0)) {
+        for (int k = 2; k <= dc3::kMaxSplit; k++) {
+            p->ksplit_max_tiles[k] = precision == LZB_FP16 ? ksplit_resident_clusters<__half>(2 * k)
+                                                            : ksplit_resident_clusters<__nv_bfloat16>(2 * k);
+        }
+    }
     p->layers.resize(1 + 2 * blocks);
     *out = p;
     return LZB_OK;

@@ -319,6 +319,35 @@ def test_single_cta_and_cta_pair_kernels_agree(lzb, W, monkeypatch):
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
 
 
+@pytest.mark.parametrize("filters,n", [(128, 5), (192, 3), (256, 1), (256, 8)])
+def test_reduction_split_kernel_agrees_with_sliced_kernel(lzb, oracle, W, monkeypatch, filters, n):
+    """Small batches run each tile on one cluster whose CTA pairs split the
+    input channels and add their partial sums through distributed shared
+    memory; LZB_CONV_KSPLIT=0 keeps them on the CTA-pair kernel with sliced
+    output channels.  Same operands, different order of the fp32 additions:
+    the raw head planes agree to fp16 rounding, and both hold the 16-bit
+    tolerances against the oracle."""
+    net = W.synthetic_network(4, filters, 2070 + filters, calibrated=True)
+    x = W.synthetic_positions(n, 1070 + n)
+    _, _, rp, rw = _reference(oracle, net, x)
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("LZB_CONV_KSPLIT", flag)
+        pipe = lzb.Pipe(net, "fp16")
+        ctx = pipe.context(n)
+        outs.append(ctx.forward(x))
+        policy, win = ctx.forward_heads(x)
+        ep, ew, _ = _errors(oracle, policy, win, rp, rw)
+        assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16, flag
+        again = ctx.forward(x)
+        assert np.array_equal(again[0], outs[-1][0]) and np.array_equal(again[1], outs[-1][1]), flag
+        ctx.close()
+        pipe.close()
+    scale = max(np.abs(outs[1][0]).max(), np.abs(outs[1][1]).max(), 1.0)
+    assert np.abs(outs[0][0] - outs[1][0]).max() <= 1e-2 * scale
+    assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-2 * scale
+
+
 def test_untransformed_filters_and_packed_positions(lzb, oracle, W):
     """The two data formats either side of the path: filters as they stand in a
     weights file (transformed on the GPU, or used directly by the convolution
