@@ -164,22 +164,27 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
     const int half_n = Kp >> 1;                        // weight rows each CTA stages per tap
     const int m0 = tile * kPairM + static_cast<int>(h) * kTileM;
 
+    // ------------------------------------------------ TMA producer (warp 0 of every CTA)
+    // The weights are constant, so their tiles are requested before this kernel
+    // waits for its predecessor: where the CTA got an SM early (a small layer
+    // leaves most of them free) they arrive while the previous layer still runs.
+    if (warp == 0 && lane == 0) {
+        const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
+        for (int tap = 0; tap < kTaps; ++tap) {
+            const uint32_t bf = map_to_cta(bfull_bar(tap), lead);
+            mbar_expect_tx_cluster(bf, btx);
+            tma_load_2d_pair(w_base + tap * kWStageBytes, &tmW, static_cast<int>(p) * kChunkK,
+                             tap * Kp + static_cast<int>(h) * half_n, bf);
+        }
+    }
     // inputs, residuals and outputs belong to the chain of kernels in the stream
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer (every CTA)
         if (lane == 0) {
             const uint32_t wf = map_to_cta(wfull_bar, lead);
             mbar_expect_tx_cluster(wf, kWinBytes);
             tma_load_2d_pair(win_base, &tmX, static_cast<int>(p) * kChunkK, m0 - kWinPad, wf);
-            const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
-            for (int tap = 0; tap < kTaps; ++tap) {
-                const uint32_t bf = map_to_cta(bfull_bar(tap), lead);
-                mbar_expect_tx_cluster(bf, btx);
-                tma_load_2d_pair(w_base + tap * kWStageBytes, &tmW, static_cast<int>(p) * kChunkK,
-                                 tap * Kp + static_cast<int>(h) * half_n, bf);
-            }
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer (pair leaders)
