@@ -199,7 +199,7 @@ def default_micro_batch(precision, B):
     whole batch for the direct convolution, 64 in fp32, and in the 16-bit
     Winograd modes the first count from 64 up for which the transform kernel's
     grid (FILTERS / 64 x positions) is whole waves of the SMs."""
-    if precision in ("fp16", "bf16"):
+    if precision in ("fp16", "bf16", "fp16x2", "fp16x3"):
         return B
     n = 64
     if precision != "fp32":
@@ -220,7 +220,7 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--precision", default=PRECISION,
-                    choices=["fp16", "bf16", "fp16-winograd", "bf16-winograd", "fp32"])
+                    choices=["fp16", "bf16", "fp16-winograd", "bf16-winograd", "fp32", "fp16x2", "fp16x3"])
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -329,7 +329,7 @@ def main():
         value = whole_job_rate(B, world, ms_dev)
         e2e = whole_job_rate(B, world, ms_e2e)
         g_ms, g_n = prof["contraction"]
-        winograd = args.precision != "fp16" and args.precision != "bf16"
+        winograd = args.precision not in ("fp16", "bf16", "fp16x2", "fp16x3")
         micro = args.micro_batch or default_micro_batch(args.precision, B)
         # every contraction launch but the input layer's covers one micro-batch of one tower
         # layer; the last micro-batch of a step may be shorter, so take the mean size
@@ -361,7 +361,8 @@ def main():
                 "frac_of_sustained_peak": value * FLOPS_DIRECT / 1e12 / peaks["bf16_tflops_sustained"],
                 "per_gpu_tflops": value * FLOPS_DIRECT / 1e12 / world},
             "roofline": {"kernel": ("gemm_tc_kernel (36 Winograd channel contractions, tcgen05)" if winograd
-                                    else "conv_direct2_kernel (3x3 conv + BN + residual + ReLU, implicit GEMM on tcgen05 CTA pairs)"),
+                                    else ("conv_direct2_kernel" if B > 11 else "conv_ksplit_kernel") +
+                                    " (3x3 conv + BN + residual + ReLU, implicit GEMM on tcgen05 CTA pairs)"),
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
                          "flops_per_launch": flops_per_launch, "avg_launch_ms": avg_s * 1e3,

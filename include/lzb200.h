@@ -44,12 +44,24 @@ extern "C" {
  *                      pipeline (transform, 36 batched contractions, fused
  *                      output/input transform).  3.6x fewer multiply-adds, about
  *                      4x the rounding error of the direct form.
+ *  LZB_FP16_X2         the direct convolution with every activation carried as
+ *                      two fp16 numbers, x = hi + lo, both multiplied with the
+ *                      fp16 weights (twice the MMAs of LZB_FP16): removes the
+ *                      rounding of the activations, which is what limits
+ *                      LZB_FP16 on deep networks; holds the half-precision
+ *                      bounds (policy 2e-3, winrate 5e-3) at 40 blocks.
+ *  LZB_FP16_X3         as LZB_FP16_X2 with the weights carried as hi + lo too
+ *                      (three MMAs: hi*hi + lo*hi + hi*lo): ten times closer
+ *                      to fp32 than LZB_FP16 (what remains is the accumulation
+ *                      inside the tensor cores).
  */
 #define LZB_FP32 0
 #define LZB_FP16 1
 #define LZB_BF16 2
 #define LZB_FP16_WINOGRAD 3
 #define LZB_BF16_WINOGRAD 4
+#define LZB_FP16_X2 5
+#define LZB_FP16_X3 6
 
 #define LZB_INPUT_PLANES 18
 #define LZB_SQ 361

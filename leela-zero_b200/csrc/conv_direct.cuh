@@ -140,6 +140,58 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const ui
     }
 }
 
+// The same for activations carried as two 16-bit planes, x = hi + lo: the
+// residual is the sum of its two planes, the result is split again.  The high
+// plane goes to the staging tile, the low plane is returned packed (word
+// 4 * v + h holds channels 8 * v + 2 * h, + 1) for a second store.
+template <typename T>
+__device__ __forceinline__ void epilogue_chunk_x2(const uint32_t (&r)[32], const uint4 (&rv)[4],
+                                                  const uint4 (&rl)[4], const float* s_scale,
+                                                  const float* s_bias, bool use_res, bool interior,
+                                                  unsigned char* stg_row, int lane,
+                                                  uint32_t (&lo)[16]) {
+    const T tag = T();
+    const float4* sc4 = reinterpret_cast<const float4*>(s_scale);
+    const float4* bi4 = reinterpret_cast<const float4*>(s_bias);
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        const float4 s0 = sc4[2 * v], s1 = sc4[2 * v + 1];
+        const float4 b0 = bi4[2 * v], b1 = bi4[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const float bi[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const uint32_t rr[4] = {rv[v].x, rv[v].y, rv[v].z, rv[v].w};
+        const uint32_t ll[4] = {rl[v].x, rl[v].y, rl[v].z, rl[v].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            float a = fmaf(__uint_as_float(r[8 * v + 2 * h]), sc[2 * h], bi[2 * h]);
+            float b = fmaf(__uint_as_float(r[8 * v + 2 * h + 1]), sc[2 * h + 1], bi[2 * h + 1]);
+            if (use_res) {
+                const float2 f = Vec2<T>::unpack(rr[h]);
+                const float2 g = Vec2<T>::unpack(ll[h]);
+                a += f.x + g.x;
+                b += f.y + g.y;
+            }
+            a = interior ? fmaxf(a, 0.f) : 0.f;
+            b = interior ? fmaxf(b, 0.f) : 0.f;
+            o[h] = pack2(tag, a, b);
+            const float2 hi = Vec2<T>::unpack(o[h]);
+            lo[4 * v + h] = pack2(tag, a - hi.x, b - hi.y);
+        }
+        *reinterpret_cast<uint4*>(stg_row + ((v ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+// Put a packed low plane (see epilogue_chunk_x2) into the staging tile.
+__device__ __forceinline__ void stage_low_plane(const uint32_t (&lo)[16], unsigned char* stg_row, int lane) {
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        *reinterpret_cast<uint4*>(stg_row + ((v ^ sw) << 4)) =
+            make_uint4(lo[4 * v], lo[4 * v + 1], lo[4 * v + 2], lo[4 * v + 3]);
+    }
+}
+
 // Hand the warp's staging tile to the TMA engine: rows m .. m+31, channels
 // col .. col+31 of the output.  Every lane fences its shared-memory writes
 // towards the async proxy, one lane issues the store.
@@ -436,21 +488,50 @@ __global__ void filters_to_wd_kernel(const float* __restrict__ f, T* __restrict_
     }
 }
 
+// Weights for activations carried as two 16-bit planes (and, optionally,
+// weights carried as two planes as well): Wd32[9][Kp][Cin_p] fp32 ->
+// Wd[9][Kp][planes * Cin_p], plane j holding the 16-bit rounding of w
+// ("high") or, where bit j of lo_mask is set, the rounding of what that left
+// over ("low").  The convolution over the widened input-channel axis is then
+// x_hi*w + x_lo*w [+ x_hi*w_lo].
+template <typename T>
+__global__ void widen_weights_kernel(const float* __restrict__ Wd32, T* __restrict__ Wd, int Cin_p,
+                                     int Kp, int planes, unsigned lo_mask) {
+    const size_t rows = (size_t)9 * Kp;
+    const size_t total = rows * planes * Cin_p;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int c = i % Cin_p;
+        const int j = (i / Cin_p) % planes;
+        const size_t row = i / ((size_t)Cin_p * planes);
+        const float w = Wd32[row * Cin_p + c];
+        const T hi = (T)w;
+        Wd[i] = ((lo_mask >> j) & 1u) ? (T)(w - (float)hi) : hi;
+    }
+}
+
 // 1x1 head convolutions reading the padded cell-major layout (see
 // head_conv_kernel for the arithmetic).  One warp per board cell.
+// ldx: elements per cell row of X; lo_off > 0: activations are two planes, the
+// low one lo_off elements after the high one.
 template <typename T>
 __global__ void __launch_bounds__(256) head_conv_cells_kernel(
     const T* __restrict__ X, const float* __restrict__ w, int Cp, int cells,
-    float* __restrict__ pol, float* __restrict__ val) {
+    float* __restrict__ pol, float* __restrict__ val, int ldx, int lo_off) {
     using P2 = Pair<T>;
     const int lane = threadIdx.x & 31;
     const int cell = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (cell >= cells) return;
     const int n = cell / kSq, s = cell % kSq;
-    const T* x = X + (size_t)cell_of(n, s / kBoard, s % kBoard) * Cp;
+    const T* x = X + (size_t)cell_of(n, s / kBoard, s % kBoard) * ldx;
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
     for (int c = 2 * lane; c < Cp; c += 64) {
-        const float2 v = P2::to_f2(*reinterpret_cast<const typename P2::type*>(x + c));
+        float2 v = P2::to_f2(*reinterpret_cast<const typename P2::type*>(x + c));
+        if (lo_off > 0) {
+            const float2 l = P2::to_f2(*reinterpret_cast<const typename P2::type*>(x + lo_off + c));
+            v.x += l.x;
+            v.y += l.y;
+        }
         const float2 w0 = *reinterpret_cast<const float2*>(w + c);
         const float2 w1 = *reinterpret_cast<const float2*>(w + Cp + c);
         const float2 w2 = *reinterpret_cast<const float2*>(w + 2 * Cp + c);

@@ -109,24 +109,31 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
 // unit of its own; used when there are fewer tiles than CTA pairs, so that a
 // small batch spreads over more SMs.
 //
+// achunks : 64-channel chunks the activation tensor has; weight chunk c >= achunks
+// is paired with activation chunk c - achunks (the weights may repeat the activations
+// against a second, "low" set of weight planes).  kPlanes : 1, or 2 when the
+// activations are carried as two 16-bit planes (high in channels [0, Kp), low in
+// [Kp, 2 Kp) of tmO and res, see epilogue_chunk_x2).
+//
 // The kernel is launched with programmatic stream serialization: it lets its
 // successor start at once (griddepcontrol.launch_dependents) and itself waits
 // for its predecessor's results only after its own set-up (barriers, tensor
 // memory, batch-norm constants), which takes that set-up off the critical path
 // of a chain of small layers.
-template <typename T>
+template <typename T, int kPlanes, bool kSliced>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_direct2_kernel(
     const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
     const __grid_constant__ CUtensorMap tmO, const T* res, const float* __restrict__ bn_mean,
     const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int npairs, int nsplit,
-    int* err) {
+    int* err, int achunks) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (base - raw);
-    const bool sliced = nsplit > 1;
-    const int nwin = sliced ? kWinBufsSliced : kWinBufs;
-    const int nstages = sliced ? kB2StagesSliced : kB2Stages;
+    // kSliced (nsplit > 1) selects the shared-memory layout at compile time, so
+    // that the loops of the whole-tile case keep constant bounds
+    constexpr int nwin = kSliced ? kWinBufsSliced : kWinBufs;
+    constexpr int nstages = kSliced ? kB2StagesSliced : kB2Stages;
     const uint32_t win_base = base;
     const uint32_t b_base = base + static_cast<uint32_t>(nwin) * kWinBytes;
     unsigned char* stage_out = smem + kOperand2Bytes;
@@ -190,7 +197,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     const int half_n = n_slice >> 1;          // weight rows each CTA stages
     // taps whose weight slices share one stage of the ring (1 for whole tiles)
     const int taps_per_stage =
-        sliced ? ((kMaxN / 2) / half_n < kMaxTapsPerStage ? (kMaxN / 2) / half_n : kMaxTapsPerStage) : 1;
+        kSliced ? ((kMaxN / 2) / half_n < kMaxTapsPerStage ? (kMaxN / 2) / half_n : kMaxTapsPerStage) : 1;
 
     // Activations, residuals and outputs belong to the chain of kernels in the
     // stream: nobody touches them before the previous kernel has finished.
@@ -214,7 +221,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                     if (!ok) break;
                     const uint32_t wf = map_to_cta(wfull_bar(wb), 0);
                     mbar_expect_tx_cluster(wf, kWinBytes);
-                    tma_load_2d_pair(win_base + wb * kWinBytes, &tmX, c * kChunkK, m0 - kWinPad, wf);
+                    tma_load_2d_pair(win_base + wb * kWinBytes, &tmX,
+                                     (c < achunks ? c : c - achunks) * kChunkK, m0 - kWinPad, wf);
                     if (++wb == nwin) { wb = 0; wphase ^= 1u; }
                     for (int tap = 0; tap < 9; tap += taps_per_stage) {
                         const int g = 9 - tap < taps_per_stage ? 9 - tap : taps_per_stage;
@@ -307,35 +315,49 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             if (!ok) break;
             tcgen05_fence_after();
             const bool use_res = (res != nullptr) && interior;
-            const T* rrow = res + static_cast<size_t>(q) * Kp + col0;
+            constexpr bool two = kPlanes == 2;
+            const T* rrow = res + static_cast<size_t>(q) * (two ? 2 * Kp : Kp) + col0;
             // accumulator columns are numbered within the slice
             const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) +
                                     static_cast<uint32_t>(acc * kMaxN + wcol);
             uint32_t ra[32], rb[32];
-            uint4 va[4], vb[4];
+            uint4 va[4], vb[4], la[4], lb[4];
+            // batch-norm etc. of one 32-channel chunk and its store(s)
+            auto emit = [&](const uint32_t (&r)[32], const uint4 (&v)[4], const uint4 (&l)[4], int col) {
+                wait_staged_tile_read(lane);
+                if constexpr (!two) {
+                    epilogue_chunk<T>(r, v, s_scale + col, s_bias + col, use_res, interior, stg_row, lane);
+                    store_staged_tile(&tmO, stg, col, row0, lane);
+                } else {
+                    uint32_t lo[16];
+                    epilogue_chunk_x2<T>(r, v, l, s_scale + col, s_bias + col, use_res, interior, stg_row,
+                                         lane, lo);
+                    store_staged_tile(&tmO, stg, col, row0, lane);
+                    wait_staged_tile_read(lane);
+                    stage_low_plane(lo, stg_row, lane);
+                    store_staged_tile(&tmO, stg, Kp + col, row0, lane);
+                }
+            };
             load_residual(va, rrow, use_res);
+            if constexpr (two) load_residual(la, rrow + Kp, use_res);
             LZB_TMEM_LD32(ra, taddr0);
             for (int j = 0; j < ncols; j += 64) {
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const bool more = j + 32 < ncols;
                 if (more) {
                     load_residual(vb, rrow + j + 32, use_res);
+                    if constexpr (two) load_residual(lb, rrow + Kp + j + 32, use_res);
                     LZB_TMEM_LD32(rb, taddr0 + j + 32);
                 }
-                wait_staged_tile_read(lane);
-                epilogue_chunk<T>(ra, va, s_scale + col0 + j, s_bias + col0 + j, use_res, interior,
-                                  stg_row, lane);
-                store_staged_tile(&tmO, stg, col0 + j, row0, lane);
+                emit(ra, va, la, col0 + j);
                 if (more) {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (j + 64 < ncols) {
                         load_residual(va, rrow + j + 64, use_res);
+                        if constexpr (two) load_residual(la, rrow + Kp + j + 64, use_res);
                         LZB_TMEM_LD32(ra, taddr0 + j + 64);
                     }
-                    wait_staged_tile_read(lane);
-                    epilogue_chunk<T>(rb, vb, s_scale + col0 + j + 32, s_bias + col0 + j + 32, use_res,
-                                      interior, stg_row, lane);
-                    store_staged_tile(&tmO, stg, col0 + j + 32, row0, lane);
+                    emit(rb, vb, lb, col0 + j + 32);
                 }
             }
             tcgen05_fence_before();

@@ -117,7 +117,9 @@ struct Layer {
     int cin_p = 0;
     bool present = false;
     CUtensorMap tmU;
-    void* Wd = nullptr;         // direct path: [9][Kp][cin_p] storage type
+    void* Wd = nullptr;         // direct path: [9][Kp][cinw] storage type
+    int cinw = 0;               // input-channel extent of Wd: cin_p x weight planes
+    int achunks = 0;            // 64-channel chunks of the activation tensor this layer reads
     CUtensorMap tmW;            // box 64 x Kp   (one CTA per tile)
     CUtensorMap tmW2[5];        // CTA pairs: [ns] has box 64 x Kp/(2*ns), ns = 1..4 where valid
     bool split_ok[5] = {false, false, false, false, false};
@@ -140,6 +142,8 @@ struct lzb_pipe {
     int precision = LZB_FP16;   // storage type: LZB_FP32, LZB_FP16 or LZB_BF16
     bool direct = false;        // true: implicit-GEMM convolution; false: Winograd pipeline
     bool pairs = false;         // direct path on CTA pairs (tcgen05 cta_group::2)
+    int aplanes = 1;            // 2: activations carried as hi + lo planes (LZB_FP16_X2, _X3)
+    bool wsplit = false;        // weights carried as hi + lo planes as well (LZB_FP16_X3)
     int elt = 2;        // bytes per stored element
     int sm_count = 0;
     // Reduction-split kernel (conv_direct3.cuh): most tiles one launch may have
@@ -370,8 +374,8 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
         const int max_clusters = p->sm_count / 2;
         // Few tiles (small batches) and a tower layer: split the reduction of
         // each tile over the pairs of one cluster.
-        const int kchunks = L.cin_p / tc::kChunkK;
-        if (kchunks >= 2 && kchunks <= dc3::kMaxSplit && p->Cp == kchunks * dc3::kGroupCols &&
+        const int kchunks = L.cinw / tc::kChunkK;
+        if (p->aplanes == 1 && kchunks >= 2 && kchunks <= dc3::kMaxSplit && p->Cp == kchunks * dc3::kGroupCols &&
             npairs <= p->ksplit_max_tiles[kchunks]) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(npairs * 2 * kchunks);
@@ -426,9 +430,12 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
         cudaError_t le;
         {
             LaunchScope scope(c, kClassContraction);
-            le = cudaLaunchKernelEx(&cfg, dc2::conv_direct2_kernel<T>, tm_in, L.tmW2[nsplit], tm_out, res,
+            auto kernel = p->aplanes == 2
+                              ? (nsplit > 1 ? dc2::conv_direct2_kernel<T, 2, true> : dc2::conv_direct2_kernel<T, 2, false>)
+                              : (nsplit > 1 ? dc2::conv_direct2_kernel<T, 1, true> : dc2::conv_direct2_kernel<T, 1, false>);
+            le = cudaLaunchKernelEx(&cfg, kernel, tm_in, L.tmW2[nsplit], tm_out, res,
                                     (const float*)L.mean, (const float*)L.invstd, Q, p->Cp,
-                                    L.cin_p / tc::kChunkK, npairs, nsplit, c->d_err);
+                                    kchunks, npairs, nsplit, c->d_err, L.achunks);
         }
         LZB_CUDA(le);
         LZB_CUDA(cudaGetLastError());
@@ -468,8 +475,9 @@ int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, fl
     const int cells = nb * kSq;
     {
         LaunchScope scope(c, kClassHead);
-        dc::head_conv_cells_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(X, p->head_w, p->Cp, cells,
-                                                                              pol_dev, val_dev);
+        dc::head_conv_cells_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(
+            X, p->head_w, p->Cp, cells, pol_dev, val_dev, p->Cp * p->aplanes,
+            p->aplanes == 2 ? p->Cp : 0);
     }
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
@@ -523,10 +531,18 @@ int set_smem_attrs() {
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc::kDSmemBytes));
     LZB_CUDA(cudaFuncSetAttribute(dc::conv_direct_kernel<__nv_bfloat16>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc::kDSmemBytes));
-    LZB_CUDA(cudaFuncSetAttribute(dc2::conv_direct2_kernel<__half>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
-    LZB_CUDA(cudaFuncSetAttribute(dc2::conv_direct2_kernel<__nv_bfloat16>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
+    {
+        const void* variants[] = {
+            (const void*)dc2::conv_direct2_kernel<__half, 1, false>, (const void*)dc2::conv_direct2_kernel<__half, 1, true>,
+            (const void*)dc2::conv_direct2_kernel<__half, 2, false>, (const void*)dc2::conv_direct2_kernel<__half, 2, true>,
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, false>,
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, true>,
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 2, false>,
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 2, true>};
+        for (const void* k : variants) {
+            LZB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
+        }
+    }
     LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__half>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc3::kD3SmemBytes));
     LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__nv_bfloat16>,
@@ -696,12 +712,34 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
     cudaError_t e = cudaMemcpy(src_dev, src, n_src * sizeof(float), cudaMemcpyHostToDevice);
     int rc = LZB_OK;
     if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("weight upload: ") + cudaGetErrorString(e));
+    // Direct path: the weight planes along the input-channel axis.  One plane
+    // normally; with two activation planes the weights repeat for the low plane,
+    // and a low weight plane (against the high activations) follows if asked for.
+    // The network input (layer 0) is exact in 16 bits and has no low plane.
+    int wplanes = 1;
+    unsigned lo_mask = 0;
+    if (p->direct) {
+        const int act_planes = (p->aplanes == 2 && layer > 0) ? 2 : 1;
+        wplanes = act_planes + (p->wsplit ? 1 : 0);
+        if (p->wsplit) lo_mask = 1u << (wplanes - 1);
+        L.cinw = L.cin_p * wplanes;
+        L.achunks = L.cin_p * act_planes / 64;
+    }
+    float* Wd32 = nullptr;           // fp32 filters in the implicit-GEMM layout (widened modes)
     if (rc == LZB_OK && p->direct && src_is_filters) {
         // plain filters into the implicit-GEMM layout, no transform involved
-        const size_t n = (size_t)9 * p->Cp * L.cin_p * p->elt;
+        const size_t n = (size_t)9 * p->Cp * L.cinw * p->elt;
         e = cudaMalloc(&L.Wd, n);
         if (e == cudaSuccess) e = cudaMemset(L.Wd, 0, n);
-        if (e == cudaSuccess) {
+        if (e == cudaSuccess && p->aplanes == 2) {
+            const size_t n32 = (size_t)9 * p->Cp * L.cin_p * sizeof(float);
+            e = cudaMalloc(&Wd32, n32);
+            if (e == cudaSuccess) e = cudaMemset(Wd32, 0, n32);
+            if (e == cudaSuccess) {
+                dc::filters_to_wd_kernel<float><<<256, 256>>>(src_dev, Wd32, c_in, K, L.cin_p, p->Cp);
+                e = cudaGetLastError();
+            }
+        } else if (e == cudaSuccess) {
             if (p->precision == LZB_FP16) {
                 dc::filters_to_wd_kernel<__half><<<256, 256>>>(src_dev, static_cast<__half*>(L.Wd), c_in, K,
                                                                L.cin_p, p->Cp);
@@ -724,7 +762,18 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
             u_dev = U32;
         }
         if (rc == LZB_OK) {
-            if (p->direct) {
+            if (p->direct && p->aplanes == 2) {
+                const size_t n32 = (size_t)9 * p->Cp * L.cin_p * sizeof(float);
+                e = cudaMalloc(&Wd32, n32);
+                if (e == cudaSuccess) e = cudaMemset(Wd32, 0, n32);
+                if (e == cudaSuccess) e = cudaMalloc(&L.Wd, (size_t)9 * p->Cp * L.cinw * p->elt);
+                if (e == cudaSuccess) {
+                    dc::untransform_u_kernel<float><<<256, 256>>>(u_dev, Wd32, c_in, p->channels, L.cin_p,
+                                                                  p->Cp);
+                    e = cudaGetLastError();
+                }
+                if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("filter upload: ") + cudaGetErrorString(e));
+            } else if (p->direct) {
                 rc = p->precision == LZB_FP16 ? upload_layer_direct_t<__half>(p, L, u_dev, c_in)
                                               : upload_layer_direct_t<__nv_bfloat16>(p, L, u_dev, c_in);
             } else if (p->precision == LZB_FP32) {
@@ -736,21 +785,28 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
             }
         }
     }
+    if (rc == LZB_OK && Wd32 != nullptr) {
+        dc::widen_weights_kernel<__half><<<512, 256>>>(Wd32, static_cast<__half*>(L.Wd), L.cin_p, p->Cp,
+                                                       wplanes, lo_mask);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("weight planes: ") + cudaGetErrorString(e));
+    }
     if (rc == LZB_OK) {
         e = cudaDeviceSynchronize();
         if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("weight repack: ") + cudaGetErrorString(e));
     }
     cudaFree(src_dev);
     cudaFree(U32);
+    cudaFree(Wd32);
     if (rc) return rc;
     if ((rc = upload_padded(&L.mean, bn_mean, p->channels, p->Cp))) return rc;
     if ((rc = upload_padded(&L.invstd, bn_invstd, p->channels, p->Cp))) return rc;
     if (p->direct) {
-        rc = make_map_2d(&L.tmW, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p, p->Cp);
+        rc = make_map_2d(&L.tmW, p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cinw, p->Cp);
         for (int ns = 1; ns <= 4 && !rc; ns++) {
             // a channel slice must be a multiple of 64 (two epilogue warps x 32 columns)
             if (p->Cp % ns != 0 || (p->Cp / ns) % 64 != 0) continue;
-            rc = make_map_2d(&L.tmW2[ns], p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cin_p,
+            rc = make_map_2d(&L.tmW2[ns], p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cinw,
                              p->Cp / (2 * ns));
             L.split_ok[ns] = (rc == LZB_OK);
         }
@@ -798,10 +854,17 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     if (!out) return fail(LZB_ERR_ARG, "null out");
     *out = nullptr;
     if (channels < 1 || blocks < 0) return fail(LZB_ERR_ARG, "bad channels/blocks");
-    bool direct = false;
+    bool direct = false, wsplit = false;
+    int aplanes = 1;
     switch (precision) {
         case LZB_FP32: break;
         case LZB_FP16: case LZB_BF16: direct = true; break;
+        case LZB_FP16_X2: case LZB_FP16_X3:
+            aplanes = 2;
+            wsplit = (precision == LZB_FP16_X3);
+            precision = LZB_FP16;
+            direct = true;
+            break;
         case LZB_FP16_WINOGRAD: precision = LZB_FP16; break;
         case LZB_BF16_WINOGRAD: precision = LZB_BF16; break;
         default: return fail(LZB_ERR_ARG, "unknown precision");
@@ -826,14 +889,17 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     p->blocks = blocks;
     p->precision = precision;
     p->direct = direct;
+    p->aplanes = aplanes;
+    p->wsplit = wsplit;
     // CTA pairs are the default; LZB_CONV_PAIRS=0 selects the one-CTA-per-tile
     // kernel (kept as a cross-check and for diagnostics).
-    p->pairs = direct && !(getenv("LZB_CONV_PAIRS") != nullptr && atoi(getenv("LZB_CONV_PAIRS")) == 0);
+    p->pairs = direct && (aplanes == 2 ||
+                          !(getenv("LZB_CONV_PAIRS") != nullptr && atoi(getenv("LZB_CONV_PAIRS")) == 0));
     p->elt = precision == LZB_FP32 ? 4 : 2;
     p->sm_count = prop.multiProcessorCount;
     // LZB_CONV_KSPLIT=0 keeps small batches on the sliced CTA-pair kernel
     // (cross-check and diagnostics).
-    if (p->pairs && !(getenv("LZB_CONV_KSPLIT") != nullptr && atoi(getenv("LZB_CONV_KSPLIT")) == 0)) {
+    if (p->pairs && aplanes == 1 && !(getenv("LZB_CONV_KSPLIT") != nullptr && atoi(getenv("LZB_CONV_KSPLIT")) == 0)) {
         for (int k = 2; k <= dc3::kMaxSplit; k++) {
             p->ksplit_max_tiles[k] = precision == LZB_FP16 ? ksplit_resident_clusters<__half>(2 * k)
                                                             : ksplit_resident_clusters<__nv_bfloat16>(2 * k);
@@ -963,8 +1029,8 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
         c->micro = c->micro_cap;
         c->Qa = round_up(static_cast<int>(dc::cells_for(c->micro_cap)), dc::kTileM);
         alloc(&c->IN, (size_t)c->Qa * 64 * p->elt);
-        alloc(&c->X, (size_t)c->Qa * p->Cp * p->elt);
-        alloc(&c->H, (size_t)c->Qa * p->Cp * p->elt);
+        alloc(&c->X, (size_t)c->Qa * p->Cp * p->aplanes * p->elt);
+        alloc(&c->H, (size_t)c->Qa * p->Cp * p->aplanes * p->elt);
     } else {
         c->micro = default_micro_batch(p, c->micro_cap);
         c->Pa = round_up(c->micro_cap * kTilesPerPos, 128);
@@ -991,11 +1057,12 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
     *c->h_err = 0;
     if (p->direct) {
         int rc = make_map_2d(&c->tmIN, p->precision, c->IN, (uint64_t)c->Qa, 64, dc::kWinRows);
-        if (!rc) rc = make_map_2d(&c->tmX, p->precision, c->X, (uint64_t)c->Qa, p->Cp, dc::kWinRows);
-        if (!rc) rc = make_map_2d(&c->tmH, p->precision, c->H, (uint64_t)c->Qa, p->Cp, dc::kWinRows);
-        if (!rc) rc = make_map_2d(&c->tmXo, p->precision, c->X, (uint64_t)c->Qa, p->Cp, 32, 32,
+        const uint64_t xp = (uint64_t)p->Cp * p->aplanes;     // channels of a cell row: hi [+ lo] plane
+        if (!rc) rc = make_map_2d(&c->tmX, p->precision, c->X, (uint64_t)c->Qa, xp, dc::kWinRows);
+        if (!rc) rc = make_map_2d(&c->tmH, p->precision, c->H, (uint64_t)c->Qa, xp, dc::kWinRows);
+        if (!rc) rc = make_map_2d(&c->tmXo, p->precision, c->X, (uint64_t)c->Qa, xp, 32, 32,
                                   CU_TENSOR_MAP_SWIZZLE_64B);
-        if (!rc) rc = make_map_2d(&c->tmHo, p->precision, c->H, (uint64_t)c->Qa, p->Cp, 32, 32,
+        if (!rc) rc = make_map_2d(&c->tmHo, p->precision, c->H, (uint64_t)c->Qa, xp, 32, 32,
                                   CU_TENSOR_MAP_SWIZZLE_64B);
         if (rc) {
             lzb_ctx_destroy(c);
@@ -1333,6 +1400,9 @@ int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n, const floa
     if (layer < 0 || layer >= (int)c->pipe->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
     if (!in || !out) return fail(LZB_ERR_ARG, "null buffer");
     LZB_CUDA(enter_device(c->pipe->device));
+    if (c->pipe->aplanes == 2) {
+        return fail(LZB_ERR_ARG, "single-layer diagnostics are not available in the two-plane modes");
+    }
     if (c->pipe->direct) {
         return c->pipe->precision == LZB_FP16
                    ? debug_conv_direct_t<__half>(c, layer, in, n, residual, out)

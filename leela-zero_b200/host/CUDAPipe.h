@@ -46,7 +46,8 @@
 
 class CUDAPipe : public ForwardPipe {
 public:
-    enum class Precision { FP32 = 0, FP16 = 1, BF16 = 2, FP16_WINOGRAD = 3, BF16_WINOGRAD = 4 };
+    enum class Precision { FP32 = 0, FP16 = 1, BF16 = 2, FP16_WINOGRAD = 3, BF16_WINOGRAD = 4,
+                           FP16_X2 = 5, FP16_X3 = 6 };
 
     // What runs a batch.  The production backend calls the lzb200 C ABI; tests
     // substitute their own to exercise the scheduler without a GPU.

@@ -197,6 +197,38 @@ def test_config3_40x256_batch256(lzb, oracle, W):
     policy, win = lzb.Pipe(net, "fp32").context(256).forward_heads(x[:16])
     ep, ew, l2 = _errors(oracle, policy, win, rp[:16], rw[:16])
     assert ep.max() <= TOL_FP32 and ew.max() <= TOL_FP32
+    # activations carried as hi + lo fp16 planes: the half-precision bounds hold
+    # for EVERY position at this depth (twice the MMAs of "fp16")
+    policy, win = lzb.Pipe(net, "fp16x2").context(256).forward_heads(x)
+    ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
+    assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16 and l2 <= SELFCHECK_MAX
+    # weights as hi + lo too: an order of magnitude closer than "fp16"
+    policy, win = lzb.Pipe(net, "fp16x3").context(64).forward_heads(x[:64])
+    ep, ew, l2 = _errors(oracle, policy, win, rp[:64], rw[:64])
+    assert ep.max() <= 4e-4 and ew.max() <= 1e-3
+
+
+@pytest.mark.parametrize("blocks,filters,n", [(1, 8, 3), (3, 64, 9), (10, 128, 8), (6, 192, 33), (20, 256, 5)])
+def test_two_plane_modes(lzb, oracle, W, blocks, filters, n):
+    """fp16x2 / fp16x3 on shallow and deep networks, small and medium batches,
+    from Winograd-transformed weights and from plain filters: always inside the
+    half-precision bounds, fp16x3 ten times inside; results do not depend on
+    where the weights came from beyond fp32 rounding of the filter recovery."""
+    net = W.synthetic_network(blocks, filters, 2090 + filters, calibrated=True)
+    x = W.synthetic_positions(n, 1090 + n)
+    _, _, rp, rw = _reference(oracle, net, x)
+    for mode, tp, tv in (("fp16x2", TOL_POLICY_16, TOL_VALUE_16), ("fp16x3", 2e-4, 5e-4)):
+        ctx = lzb.Pipe(net, mode).context(n)
+        policy, win = ctx.forward_heads(x)
+        ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
+        assert ep.max() <= tp and ew.max() <= tv and l2 <= SELFCHECK_MAX, mode
+        p2, w2 = lzb.Pipe(net, mode, from_filters=True).context(n).forward_heads(x)
+        assert np.abs(p2 - policy).max() <= tp and np.abs(w2 - win).max() <= tv, mode
+        one = ctx.forward_heads(x[:1])
+        assert np.abs(one[0] - policy[:1]).max() <= tp and np.abs(one[1] - win[:1]).max() <= tv, mode
+        with pytest.raises(lzb.LzbError):
+            ctx.debug_conv(0, x)
+
 
 
 def test_literal_deep_network_fp32(lzb, oracle, W):
