@@ -190,7 +190,9 @@ std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out, int gpu_index)
                                   (m_queue.size() >= full || m_in_flight[gpu_index] < 2));
         });
         if (!m_running) return batch;
-        if (m_queue.size() < full && m_gather_us > 0) {
+        // A lone caller (one request now, one in the previous batch) gains
+        // nothing from the window; everybody else does.
+        if (m_queue.size() < full && m_gather_us > 0 && (m_queue.size() > 1 || m_last_batch > 1)) {
             m_gathering = true;
             m_cv.wait_for(lk, std::chrono::microseconds(m_gather_us),
                           [&] { return !m_running || m_queue.size() >= full; });
@@ -200,6 +202,7 @@ std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out, int gpu_index)
         count = std::min(m_queue.size(), full);
         if (count == 0) continue;          // drained while gathering
         *timed_out = count < full;
+        m_last_batch = count;
         m_in_flight[gpu_index]++;
         batch.assign(m_queue.begin(), m_queue.begin() + count);
         m_queue.erase(m_queue.begin(), m_queue.begin() + count);

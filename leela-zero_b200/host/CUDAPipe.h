@@ -144,6 +144,7 @@ private:
     int m_gather_us = 100;
     std::vector<int> m_in_flight;       // EAGER: per GPU, batches picked up and not yet finished
     bool m_gathering = false;           // EAGER: a worker is inside its gathering window
+    std::size_t m_last_batch = 0;       // EAGER: positions in the batch picked up last
     std::atomic<int> m_live_gpus{0};
     std::vector<char> m_gpu_failed;     // per GPU, guarded by m_mutex
     std::vector<std::thread> m_threads;

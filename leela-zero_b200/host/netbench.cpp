@@ -7,7 +7,7 @@
 // requested shape (throughput does not depend on their values).
 //
 //   netbench [--blocks B] [--filters C] [--threads T] [--batch S] [--gpus G]
-//            [--iterations N] [--precision fp32|fp16|bf16]
+//            [--iterations N] [--precision fp32|fp16|bf16|fp16x2] [--batching wait|eager]
 #include <atomic>
 #include <chrono>
 #include <cstdio>
@@ -23,6 +23,7 @@
 int main(int argc, char** argv) {
     int blocks = 15, filters = 192, threads = 64, batch = 8, gpus = 1, iterations = 16000;
     CUDAPipe::Precision precision = CUDAPipe::Precision::FP16;
+    bool eager = false;
     for (int i = 1; i + 1 < argc; i += 2) {
         const std::string k = argv[i], v = argv[i + 1];
         if (k == "--blocks") blocks = std::atoi(v.c_str());
@@ -33,7 +34,10 @@ int main(int argc, char** argv) {
         else if (k == "--iterations") iterations = std::atoi(v.c_str());
         else if (k == "--precision") {
             precision = v == "fp32" ? CUDAPipe::Precision::FP32
-                                    : v == "bf16" ? CUDAPipe::Precision::BF16 : CUDAPipe::Precision::FP16;
+                        : v == "bf16" ? CUDAPipe::Precision::BF16
+                        : v == "fp16x2" ? CUDAPipe::Precision::FP16_X2 : CUDAPipe::Precision::FP16;
+        } else if (k == "--batching") {
+            eager = (v == "eager");
         } else {
             std::fprintf(stderr, "unknown option %s\n", k.c_str());
             return 2;
@@ -63,6 +67,7 @@ int main(int argc, char** argv) {
     for (int g = 0; g < gpus; g++) ids.push_back(g);
     try {
         CUDAPipe pipe(ids, batch, threads, precision);
+        if (eager) pipe.set_batching(CUDAPipe::Batching::EAGER);
         pipe.initialize(filters);
         pipe.push_weights(6, 18, filters, w);
         std::atomic<int> runcount{0};
@@ -90,9 +95,9 @@ int main(int argc, char** argv) {
         std::printf("%5d evaluations in %5.2f seconds -> %d n/s\n", runcount.load(), sec,
                     static_cast<int>(runcount.load() / sec));
         std::printf("{\"evals_per_s\": %.1f, \"blocks\": %d, \"filters\": %d, \"threads\": %d, "
-                    "\"batch\": %d, \"gpus\": %d, \"batches\": %zu, \"mean_batch\": %.2f, "
+                    "\"batch\": %d, \"batching\": \"%s\", \"gpus\": %d, \"batches\": %zu, \"mean_batch\": %.2f, "
                     "\"full_batches\": %zu, \"timeouts\": %zu, \"wait_ms\": %d}\n",
-                    runcount.load() / sec, blocks, filters, threads, batch, gpus, s.batches,
+                    runcount.load() / sec, blocks, filters, threads, batch, eager ? "eager" : "wait", gpus, s.batches,
                     s.batches ? double(s.positions) / s.batches : 0.0, s.full_batches, s.timeouts,
                     s.wait_ms);
     } catch (const std::exception& e) {
