@@ -194,6 +194,24 @@ def run_reference(args):
     }))
 
 
+def calibrated_raw_network(W, blocks, filters, seed, rank, world):
+    """The benchmark network on every rank.  Each rank draws the same raw
+    network from the seed; the batch-norm calibration pass (a few seconds of
+    CPU) runs on rank 0 only and its statistics are handed to the other ranks
+    through the process group."""
+    raw = W.synthetic_raw_network(blocks, filters, seed)
+    bn_keys = ("bn_mean", "bn_var", "bn_pol_mean", "bn_pol_var", "bn_val_mean", "bn_val_var")
+    stats = [None]
+    if rank == 0:
+        cal = W.calibrate_batchnorm(raw, W.synthetic_positions(4, seed + 1))
+        stats = [{k: cal[k] for k in bn_keys}]
+    if world > 1:
+        import torch.distributed as dist
+        dist.broadcast_object_list(stats, src=0)
+    raw.update(stats[0])
+    return raw
+
+
 def default_micro_batch(precision, B):
     """Positions per pass through the tower as the library chooses them: the
     whole batch for the direct convolution, 64 in fp32, and in the 16-bit
@@ -239,18 +257,7 @@ def main():
 
     pkg = load_package()
     W = pkg.weights
-    # Every rank draws the same raw network from the seed; the batch-norm
-    # calibration pass (a few seconds of CPU) runs on rank 0 only and its
-    # statistics are handed to the other ranks.
-    raw = W.synthetic_raw_network(BLOCKS, FILTERS, WEIGHT_SEED)
-    bn_keys = ("bn_mean", "bn_var", "bn_pol_mean", "bn_pol_var", "bn_val_mean", "bn_val_var")
-    stats = [None]
-    if rank == 0:
-        cal = W.calibrate_batchnorm(raw, W.synthetic_positions(4, WEIGHT_SEED + 1))
-        stats = [{k: cal[k] for k in bn_keys}]
-    if world > 1:
-        dist.broadcast_object_list(stats, src=0)
-    raw.update(stats[0])
+    raw = calibrated_raw_network(W, BLOCKS, FILTERS, WEIGHT_SEED, rank, world)
     net = W.prepare(raw)
     pipe = pkg.Pipe(net, args.precision, device=local)
     B = args.batch

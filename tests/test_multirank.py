@@ -25,8 +25,11 @@ x = W.synthetic_positions(4, bench.INPUT_SEED + rank)       # each rank draws it
 ms = 5.0 + 3.0 * rank                                        # rank 1 is the slow one
 dist.barrier()
 slowest = bench.max_over_ranks(ms, world)
+raw = bench.calibrated_raw_network(W, 2, 16, 77, rank, world)   # calibrated on rank 0, handed over
 out = {"rank": rank, "slowest": slowest, "value": bench.whole_job_rate(256, world, slowest),
-       "checksum": float(x.sum())}
+       "checksum": float(x.sum()),
+       "bn": [float(sum(float(m.sum()) for m in raw["bn_mean"])), float(sum(float(v.sum()) for v in raw["bn_var"])),
+              float(raw["bn_val_mean"].sum())]}
 gathered = [None] * world
 dist.all_gather_object(gathered, out)
 if rank == 0:
@@ -49,6 +52,11 @@ def test_two_gloo_ranks_shard_and_take_the_slowest(tmp_path):
     assert [g["rank"] for g in got] == [0, 1]
     assert all(g["slowest"] == 8.0 for g in got)                    # max over ranks, on every rank
     assert all(abs(g["value"] - 2 * 256 / 8.0e-3) < 1e-6 for g in got)   # whole-job aggregate
+    assert got[0]["bn"] == got[1]["bn"]                              # rank 1 got rank 0's calibration
+    import bench
+    W = bench.load_package().weights
+    plain = W.synthetic_raw_network(2, 16, 77)
+    assert got[0]["bn"][1] != float(sum(float(v.sum()) for v in plain["bn_var"]))   # and it is a calibrated one
     assert got[0]["checksum"] != got[1]["checksum"]                 # different shards
 
 
