@@ -43,7 +43,7 @@ FLOPS_GEMM_PER_POS = 2 * 36 * 25 * FILTERS * FILTERS
 # algorithmic FLOPs of one 3x3 layer per position as a direct convolution (C = K = 256)
 FLOPS_CONV_PER_POS = 2 * 9 * FILTERS * FILTERS * 361
 # DRAM traffic (read + write) of one conv_direct_kernel launch at 256 positions, from the committed ncu capture
-GEMM_DRAM_BYTES_PER_LAUNCH = 90.1e6   # mean of two captured launches (68 and 112 MB), profiles/conv_direct2_kernel_40x256_batch256.md
+GEMM_DRAM_BYTES_PER_LAUNCH = 90.1e6   # mean of two captured launches (66 and 113 MB), profiles/conv_direct2_kernel_40x256_batch256.md
 
 
 def load_package():
@@ -373,7 +373,7 @@ def main():
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
                          "flops_per_launch": flops_per_launch, "avg_launch_ms": avg_s * 1e3,
-                         "traffic": GEMM_DRAM_BYTES_PER_LAUNCH},
+                         "traffic": (GEMM_DRAM_BYTES_PER_LAUNCH if args.precision == "fp16" and B == BATCH else None)},
             "kernel_time_share": {k: (v[0] / total_ms if total_ms else 0.0) for k, v in prof.items()},
             "kernel_ms_per_step": {k: v[0] / prof_steps for k, v in prof.items()},
         }

@@ -269,6 +269,21 @@ def test_ragged_batches_and_micro_batches(lzb, W, mode):
     assert np.array_equal(pol, full_pol[perm]) and np.array_equal(val, full_val[perm])
 
 
+def test_batches_beyond_the_micro_batch_capacity(lzb, W):
+    """600 positions in one call: the context cuts them into passes of at most
+    256; every position comes out as it does in a call of its own pass size."""
+    net = W.synthetic_network(2, 64, 2052, calibrated=True)
+    x = W.synthetic_positions(600, 1052)
+    ctx = lzb.Pipe(net, "fp16").context(600)
+    pol, val = ctx.forward(x)
+    for lo, hi in ((0, 256), (256, 512), (512, 600)):
+        p, v = ctx.forward(x[lo:hi])
+        assert np.array_equal(p, pol[lo:hi]) and np.array_equal(v, val[lo:hi]), lo
+    policy, win = ctx.forward_heads(x)
+    assert policy.shape == (600, 362) and np.allclose(policy.sum(1), 1.0, atol=1e-5)
+    assert np.all((win >= 0) & (win <= 1))
+
+
 def test_maximum_batch_and_repeatability(lzb, W):
     """256 positions (the largest benchmarked batch) twice: identical results;
     a blank board and a full board are evaluated without special cases."""
