@@ -25,9 +25,9 @@
 //      sums of the groups its CTA does not own from tensor memory into a send
 //      area in its own shared memory, 32 cells x 32 channels (4 KB) per block;
 //   4. cluster barrier: every pair's MMAs have retired, so the operand area of
-//      every CTA is dead and becomes its receive area; one lane per warp then
-//      sends each block to its owner with a bulk shared-to-shared::cluster copy
-//      that completes on the owner's mbarrier.  (Scattered st.shared::cluster
+//      every CTA is dead and becomes its receive area; one thread then sends
+//      each owner its eight blocks (32 KB, contiguous on both sides) with a bulk
+//      shared-to-shared::cluster copy that completes on the owner's mbarrier.  (Scattered st.shared::cluster
 //      from the tensor-memory register layout was measured first: 16-byte
 //      packets, 5 us for the 96 KB a CTA sends.)
 //   5. the owner waits for its incoming bytes, adds its own partial and the
@@ -246,16 +246,16 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
     }
     __syncwarp();
     cluster_sync_all();          // step 4: every pair's MMAs have retired; operands are dead
-    if (epi && ok && lane == 0) {
+    // one copy per owner: the eight blocks of a slot are contiguous on both sides
+    if (warp == 2 && lane == 0 && ok) {
         int gi = 0;
         for (int g = 0; g < kchunks; ++g) {
             if (g == static_cast<int>(p)) continue;
             const int slot = static_cast<int>(p) < g ? static_cast<int>(p) : static_cast<int>(p) - 1;
             const uint32_t owner = static_cast<uint32_t>(2 * g) + h;
-            bulk_copy_to_cta(
-                map_to_cta(smem_u32(recv) + static_cast<uint32_t>(slot) * kSlotBytes + blk * kBlockBytes, owner),
-                smem_u32(send) + static_cast<uint32_t>(gi) * kSlotBytes + blk * kBlockBytes, kBlockBytes,
-                map_to_cta(rfull_bar, owner));
+            bulk_copy_to_cta(map_to_cta(smem_u32(recv) + static_cast<uint32_t>(slot) * kSlotBytes, owner),
+                             smem_u32(send) + static_cast<uint32_t>(gi) * kSlotBytes, kSlotBytes,
+                             map_to_cta(rfull_bar, owner));
             ++gi;
         }
     }
