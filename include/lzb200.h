@@ -45,12 +45,15 @@ extern "C" {
  *                      output/input transform).  3.6x fewer multiply-adds, about
  *                      4x the rounding error of the direct form.
  *  LZB_FP16_X2         the direct convolution with every activation carried as
- *                      two fp16 numbers, x = hi + lo, both multiplied with the
- *                      fp16 weights (twice the MMAs of LZB_FP16): removes the
- *                      rounding of the activations, which is what limits
- *                      LZB_FP16 on deep networks; holds the half-precision
- *                      bounds (policy 2e-3, winrate 5e-3) at 40 blocks.
- *  LZB_FP16_X3         as LZB_FP16_X2 with the weights carried as hi + lo too
+ *                      x = hi + lo, hi in fp16 and lo in e5m2 (one byte); the
+ *                      fp16 plane is multiplied with the fp16 weights, the e5m2
+ *                      plane with an e5m2 copy of them (kind::f8f6f4 MMAs, half
+ *                      the time of the fp16 ones): 1.6x the cost of LZB_FP16.
+ *                      Removes the rounding of the activations, which is what
+ *                      limits LZB_FP16 on deep networks; holds the
+ *                      half-precision bounds (policy 2e-3, winrate 5e-3) for
+ *                      every position at 40 blocks.
+ *  LZB_FP16_X3         activations and weights both carried as two fp16 planes
  *                      (three MMAs: hi*hi + lo*hi + hi*lo): ten times closer
  *                      to fp32 than LZB_FP16 (what remains is the accumulation
  *                      inside the tensor cores).

@@ -192,6 +192,76 @@ __device__ __forceinline__ void stage_low_plane(const uint32_t (&lo)[16], unsign
     }
 }
 
+// ---- activations as an fp16 plane plus an e5m2 plane, x = hi + lo ----------
+// e5m2 (1-5-2) is the upper byte of an fp16 number, so both conversions are
+// byte moves around one rounding.
+__device__ __forceinline__ uint32_t e5m2_from_float(float v) {
+    const uint32_t h = __half_as_ushort(__float2half_rn(v));
+    return (h + 0x7Fu + ((h >> 8) & 1u)) >> 8;            // round to nearest even on the dropped byte
+}
+__device__ __forceinline__ float e5m2_to_float(uint32_t byte) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>((byte & 0xFFu) << 8)));
+}
+// 32 bytes (32 channels) of an e5m2 residual row, or zeros.
+__device__ __forceinline__ void load_residual8(uint4 (&v)[2], const unsigned char* src, bool use) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        v[i] = use ? reinterpret_cast<const uint4*>(src)[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+// epilogue_chunk for that form: the residual is fp16 + e5m2, the result is
+// split into an fp16 tile (written to the staging tile like epilogue_chunk
+// does) and 32 e5m2 bytes returned in lo[8] (byte c of the row = channel c).
+template <typename T>
+__device__ __forceinline__ void epilogue_chunk_e5m2(const uint32_t (&r)[32], const uint4 (&rv)[4],
+                                                    const uint4 (&rl)[2], const float* s_scale,
+                                                    const float* s_bias, bool use_res, bool interior,
+                                                    unsigned char* stg_row, int lane,
+                                                    uint32_t (&lo)[8]) {
+    const T tag = T();
+    const float4* sc4 = reinterpret_cast<const float4*>(s_scale);
+    const float4* bi4 = reinterpret_cast<const float4*>(s_bias);
+    const int sw = (lane >> 1) & 3;
+    const uint32_t lw[8] = {rl[0].x, rl[0].y, rl[0].z, rl[0].w, rl[1].x, rl[1].y, rl[1].z, rl[1].w};
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        const float4 s0 = sc4[2 * v], s1 = sc4[2 * v + 1];
+        const float4 b0 = bi4[2 * v], b1 = bi4[2 * v + 1];
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const float bi[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const uint32_t rr[4] = {rv[v].x, rv[v].y, rv[v].z, rv[v].w};
+        uint32_t o[4];
+        uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+            float a = fmaf(__uint_as_float(r[8 * v + 2 * h]), sc[2 * h], bi[2 * h]);
+            float b = fmaf(__uint_as_float(r[8 * v + 2 * h + 1]), sc[2 * h + 1], bi[2 * h + 1]);
+            if (use_res) {
+                const float2 f = Vec2<T>::unpack(rr[h]);
+                // channels 8v + 2h, +1 are bytes (2h, 2h + 1) & 3 of word 2v + h / 2
+                const uint32_t w = lw[2 * v + (h >> 1)] >> (16 * (h & 1));
+                a += f.x + e5m2_to_float(w);
+                b += f.y + e5m2_to_float(w >> 8);
+            }
+            a = interior ? fmaxf(a, 0.f) : 0.f;
+            b = interior ? fmaxf(b, 0.f) : 0.f;
+            o[h] = pack2(tag, a, b);
+            const float2 hi = Vec2<T>::unpack(o[h]);
+            const uint32_t two = e5m2_from_float(a - hi.x) | (e5m2_from_float(b - hi.y) << 8);
+            packed[h >> 1] |= two << (16 * (h & 1));
+        }
+        lo[2 * v] = packed[0];
+        lo[2 * v + 1] = packed[1];
+        *reinterpret_cast<uint4*>(stg_row + ((v ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+// The 32 x 32-byte e5m2 tile of a warp in its staging buffer, rows unswizzled.
+__device__ __forceinline__ void stage_e5m2_plane(const uint32_t (&lo)[8], unsigned char* stg, int lane) {
+    uint4* row = reinterpret_cast<uint4*>(stg + lane * 32);
+    row[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    row[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+}
+
 // Hand the warp's staging tile to the TMA engine: rows m .. m+31, channels
 // col .. col+31 of the output.  Every lane fences its shared-memory writes
 // towards the async proxy, one lane issues the store.
@@ -510,14 +580,29 @@ __global__ void widen_weights_kernel(const float* __restrict__ Wd32, T* __restri
     }
 }
 
+// The weights once more in e5m2, for the MMAs of an e5m2 activation plane:
+// Wd32[9][Kp][Cin_p] fp32 -> W8[9][Kp][Cin8] bytes, Cin8 = Cin_p rounded up to
+// 128 (one 128-byte swizzle row), zero padded.
+__global__ void weights_to_e5m2_kernel(const float* __restrict__ Wd32, unsigned char* __restrict__ W8,
+                                       int Cin_p, int Cin8, int Kp) {
+    const size_t total = (size_t)9 * Kp * Cin8;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const int c = i % Cin8;
+        const size_t row = i / Cin8;
+        W8[i] = c < Cin_p ? static_cast<unsigned char>(e5m2_from_float(Wd32[row * Cin_p + c])) : 0;
+    }
+}
+
 // 1x1 head convolutions reading the padded cell-major layout (see
 // head_conv_kernel for the arithmetic).  One warp per board cell.
-// ldx: elements per cell row of X; lo_off > 0: activations are two planes, the
-// low one lo_off elements after the high one.
+// ldx: elements (of T) per cell row of X; lo_off > 0: activations are two
+// planes, the low one lo_off elements after the high one, stored as T or,
+// with lo_e5m2, as one e5m2 byte per channel.
 template <typename T>
 __global__ void __launch_bounds__(256) head_conv_cells_kernel(
     const T* __restrict__ X, const float* __restrict__ w, int Cp, int cells,
-    float* __restrict__ pol, float* __restrict__ val, int ldx, int lo_off) {
+    float* __restrict__ pol, float* __restrict__ val, int ldx, int lo_off, int lo_e5m2) {
     using P2 = Pair<T>;
     const int lane = threadIdx.x & 31;
     const int cell = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -527,7 +612,12 @@ __global__ void __launch_bounds__(256) head_conv_cells_kernel(
     float a0 = 0.f, a1 = 0.f, a2 = 0.f;
     for (int c = 2 * lane; c < Cp; c += 64) {
         float2 v = P2::to_f2(*reinterpret_cast<const typename P2::type*>(x + c));
-        if (lo_off > 0) {
+        if (lo_off > 0 && lo_e5m2) {
+            const unsigned short two =
+                *reinterpret_cast<const unsigned short*>(reinterpret_cast<const unsigned char*>(x + lo_off) + c);
+            v.x += e5m2_to_float(two);
+            v.y += e5m2_to_float(two >> 8);
+        } else if (lo_off > 0) {
             const float2 l = P2::to_f2(*reinterpret_cast<const typename P2::type*>(x + lo_off + c));
             v.x += l.x;
             v.y += l.y;

@@ -90,6 +90,16 @@ __device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t d_tmem, uint64_t a
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// The same with e5m2 / e4m3 operands (K = 32 per instruction: again 32 bytes of every row).
+__device__ __forceinline__ void tcgen05_mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                    uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // Arrive, once the pair's MMAs issued so far have retired, on the barrier at
 // this shared-memory offset in BOTH CTAs of the pair.
 __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
@@ -113,7 +123,11 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
 // is paired with activation chunk c - achunks (the weights may repeat the activations
 // against a second, "low" set of weight planes).  kPlanes : 1, or 2 when the
 // activations are carried as two 16-bit planes (high in channels [0, Kp), low in
-// [Kp, 2 Kp) of tmO and res, see epilogue_chunk_x2).
+// [Kp, 2 Kp) of tmO and res, see epilogue_chunk_x2), or 3 when the low plane is
+// e5m2: a cell row is [Kp x 16 bits | Kp bytes]; chunks c >= achunks then come
+// from tmXl / tmWl (byte maps, 128 channels per 128-byte chunk) and are
+// multiplied by kind::f8f6f4 MMAs, and the low output plane goes out through
+// tmOl (bytes, box 32 x 32).  tmXl, tmWl, tmOl are ignored otherwise.
 //
 // The kernel is launched with programmatic stream serialization: it lets its
 // successor start at once (griddepcontrol.launch_dependents) and itself waits
@@ -125,7 +139,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
     const __grid_constant__ CUtensorMap tmO, const T* res, const float* __restrict__ bn_mean,
     const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int npairs, int nsplit,
-    int* err, int achunks) {
+    int* err, int achunks, const __grid_constant__ CUtensorMap tmXl,
+    const __grid_constant__ CUtensorMap tmWl, const __grid_constant__ CUtensorMap tmOl) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -221,8 +236,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                     if (!ok) break;
                     const uint32_t wf = map_to_cta(wfull_bar(wb), 0);
                     mbar_expect_tx_cluster(wf, kWinBytes);
-                    tma_load_2d_pair(win_base + wb * kWinBytes, &tmX,
-                                     (c < achunks ? c : c - achunks) * kChunkK, m0 - kWinPad, wf);
+                    const bool low8 = kPlanes == 3 && c >= achunks;     // e5m2 chunk: byte coordinates
+                    const int wcol = low8 ? (c - achunks) * 128 : c * kChunkK;
+                    tma_load_2d_pair(win_base + wb * kWinBytes, low8 ? &tmXl : &tmX,
+                                     low8 ? wcol : (c < achunks ? c : c - achunks) * kChunkK,
+                                     m0 - kWinPad, wf);
                     if (++wb == nwin) { wb = 0; wphase ^= 1u; }
                     for (int tap = 0; tap < 9; tap += taps_per_stage) {
                         const int g = 9 - tap < taps_per_stage ? 9 - tap : taps_per_stage;
@@ -231,8 +249,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                         const uint32_t bf = map_to_cta(bfull_bar(stage), 0);
                         mbar_expect_tx_cluster(bf, btx * static_cast<uint32_t>(g));
                         for (int j = 0; j < g; ++j) {
-                            tma_load_2d_pair(b_base + stage * kB2StageBytes + j * btx, &tmW,
-                                             c * kChunkK, (tap + j) * Kp + wrow0, bf);
+                            tma_load_2d_pair(b_base + stage * kB2StageBytes + j * btx, low8 ? &tmWl : &tmW,
+                                             wcol, (tap + j) * Kp + wrow0, bf);
                         }
                         if (++stage == nstages) { stage = 0; phase ^= 1u; }
                     }
@@ -246,6 +264,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                                    (OperandFormat<T>::value << 10) |
                                    (static_cast<uint32_t>(n_slice >> 3) << 17) |
                                    (static_cast<uint32_t>(kPairM >> 4) << 24);
+            // e5m2 x e5m2 -> fp32 for the chunks of an e5m2 activation plane
+            const uint32_t idesc8 = (1u << 4) | (1u << 7) | (1u << 10) |
+                                    (static_cast<uint32_t>(n_slice >> 3) << 17) |
+                                    (static_cast<uint32_t>(kPairM >> 4) << 24);
             int stage = 0, wb = 0;
             uint32_t phase = 0, wphase = 0;
             bool ok = true;
@@ -274,10 +296,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                                 umma_desc_sw128(win + static_cast<uint32_t>(row0) * 128u);
                             const uint64_t b_desc =
                                 umma_desc_sw128(b_base + stage * kB2StageBytes + j * btx);
+                            if (kPlanes == 3 && c >= achunks) {
 #pragma unroll
-                            for (int k = 0; k < kChunkK / 16; ++k) {
-                                tcgen05_mma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
-                                                     (c > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                                for (int k = 0; k < 4; ++k) {
+                                    tcgen05_mma_f8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc8, 1u);
+                                }
+                            } else {
+#pragma unroll
+                                for (int k = 0; k < kChunkK / 16; ++k) {
+                                    tcgen05_mma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                                                         (c > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                                }
                             }
                         }
                         tcgen05_commit_pair(bempty_bar(stage));
@@ -316,16 +345,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             tcgen05_fence_after();
             const bool use_res = (res != nullptr) && interior;
             constexpr bool two = kPlanes == 2;
-            const T* rrow = res + static_cast<size_t>(q) * (two ? 2 * Kp : Kp) + col0;
+            constexpr bool e5 = kPlanes == 3;
+            // elements of T per cell row of the residual tensor
+            const int ldr = two ? 2 * Kp : (e5 ? Kp + (Kp >> 1) : Kp);
+            const T* rrow = res + static_cast<size_t>(q) * ldr + col0;
+            // e5m2 plane of the same row: Kp bytes after the Kp 16-bit channels
+            const unsigned char* erow =
+                reinterpret_cast<const unsigned char*>(res + static_cast<size_t>(q) * ldr + Kp) + col0;
             // accumulator columns are numbered within the slice
             const uint32_t taddr0 = tmem_base + (static_cast<uint32_t>(qd * 32) << 16) +
                                     static_cast<uint32_t>(acc * kMaxN + wcol);
             uint32_t ra[32], rb[32];
-            uint4 va[4], vb[4], la[4], lb[4];
+            uint4 va[4], vb[4], la[4], lb[4], ea[2], eb[2];
             // batch-norm etc. of one 32-channel chunk and its store(s)
-            auto emit = [&](const uint32_t (&r)[32], const uint4 (&v)[4], const uint4 (&l)[4], int col) {
+            auto emit = [&](const uint32_t (&r)[32], const uint4 (&v)[4], const uint4 (&l)[4],
+                            const uint4 (&e)[2], int col) {
                 wait_staged_tile_read(lane);
-                if constexpr (!two) {
+                if constexpr (e5) {
+                    uint32_t lo[8];
+                    epilogue_chunk_e5m2<T>(r, v, e, s_scale + col, s_bias + col, use_res, interior, stg_row,
+                                           lane, lo);
+                    store_staged_tile(&tmO, stg, col, row0, lane);
+                    wait_staged_tile_read(lane);
+                    stage_e5m2_plane(lo, stg_ptr, lane);
+                    store_staged_tile(&tmOl, stg, col, row0, lane);
+                } else if constexpr (!two) {
                     epilogue_chunk<T>(r, v, s_scale + col, s_bias + col, use_res, interior, stg_row, lane);
                     store_staged_tile(&tmO, stg, col, row0, lane);
                 } else {
@@ -340,6 +384,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             };
             load_residual(va, rrow, use_res);
             if constexpr (two) load_residual(la, rrow + Kp, use_res);
+            if constexpr (e5) load_residual8(ea, erow, use_res);
             LZB_TMEM_LD32(ra, taddr0);
             for (int j = 0; j < ncols; j += 64) {
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -347,17 +392,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                 if (more) {
                     load_residual(vb, rrow + j + 32, use_res);
                     if constexpr (two) load_residual(lb, rrow + Kp + j + 32, use_res);
+                    if constexpr (e5) load_residual8(eb, erow + j + 32, use_res);
                     LZB_TMEM_LD32(rb, taddr0 + j + 32);
                 }
-                emit(ra, va, la, col0 + j);
+                emit(ra, va, la, ea, col0 + j);
                 if (more) {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (j + 64 < ncols) {
                         load_residual(va, rrow + j + 64, use_res);
                         if constexpr (two) load_residual(la, rrow + Kp + j + 64, use_res);
+                        if constexpr (e5) load_residual8(ea, erow + j + 64, use_res);
                         LZB_TMEM_LD32(ra, taddr0 + j + 64);
                     }
-                    emit(rb, vb, lb, col0 + j + 32);
+                    emit(rb, vb, lb, eb, col0 + j + 32);
                 }
             }
             tcgen05_fence_before();

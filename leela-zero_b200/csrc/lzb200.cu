@@ -90,17 +90,21 @@ EncodeTiledFn encode_tiled_fn() {
 // maps use boxes of 64 columns (128 bytes) x box_rows under the 128-byte swizzle
 // the UMMA descriptors expect; the output maps of the convolution kernel use
 // 32 x 32 boxes under the 64-byte swizzle.
+// precision < 0: a byte tensor (e5m2 planes).  pitch_bytes 0: rows are dense.
 int make_map_2d(CUtensorMap* map, int precision, void* base, uint64_t rows, uint64_t cols,
                 uint32_t box_rows, uint32_t box_cols = 64,
-                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+                CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, uint64_t pitch_bytes = 0) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(LZB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    const uint64_t elt = precision < 0 ? 1 : 2;
     const cuuint64_t dims[2] = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint64_t strides[1] = {pitch_bytes ? pitch_bytes : cols * elt};
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt =
-        precision == LZB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        precision < 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                      : (precision == LZB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
     CUresult r = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -120,6 +124,9 @@ struct Layer {
     void* Wd = nullptr;         // direct path: [9][Kp][cinw] storage type
     int cinw = 0;               // input-channel extent of Wd: cin_p x weight planes
     int achunks = 0;            // 64-channel chunks of the activation tensor this layer reads
+    unsigned char* Wd8 = nullptr;   // e5m2 copy of the weights [9][Kp][cin8] (LZB_FP16_X2), or null
+    int lchunks = 0;            // 128-channel e5m2 chunks that follow the fp16 chunks
+    CUtensorMap tmW8[5];        // byte maps over Wd8, box 128 x Kp/(2*ns)
     CUtensorMap tmW;            // box 64 x Kp   (one CTA per tile)
     CUtensorMap tmW2[5];        // CTA pairs: [ns] has box 64 x Kp/(2*ns), ns = 1..4 where valid
     bool split_ok[5] = {false, false, false, false, false};
@@ -142,7 +149,10 @@ struct lzb_pipe {
     int precision = LZB_FP16;   // storage type: LZB_FP32, LZB_FP16 or LZB_BF16
     bool direct = false;        // true: implicit-GEMM convolution; false: Winograd pipeline
     bool pairs = false;         // direct path on CTA pairs (tcgen05 cta_group::2)
-    int aplanes = 1;            // 2: activations carried as hi + lo planes (LZB_FP16_X2, _X3)
+    int aplanes = 1;            // activations carried as hi + lo: 2 = two 16-bit planes (LZB_FP16_X3),
+                                // 3 = a 16-bit plane and an e5m2 plane (LZB_FP16_X2)
+    // bytes of one cell row of the activation tensors
+    int row_bytes() const { return aplanes == 3 ? 3 * Cp : aplanes * Cp * elt; }
     bool wsplit = false;        // weights carried as hi + lo planes as well (LZB_FP16_X3)
     int elt = 2;        // bytes per stored element
     int sm_count = 0;
@@ -176,6 +186,8 @@ struct lzb_ctx {
     void *IN = nullptr, *H = nullptr;
     CUtensorMap tmIN, tmX, tmH;      // window loads
     CUtensorMap tmXo, tmHo;          // 32 x 32 output stores
+    CUtensorMap tmXl, tmHl;          // e5m2 planes of X and H: 128-byte windows (LZB_FP16_X2)
+    CUtensorMap tmXlo, tmHlo;        // ... and their 32 x 32-byte output stores
     long long launches = 0;
     // per-launch timing (diagnostics): event pairs tagged with a kernel class
     bool profiling = false;
@@ -366,7 +378,8 @@ int run_tower(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* va
 
 template <typename T>
 int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm_in,
-                       const CUtensorMap& tm_out, const T* res) {
+                       const CUtensorMap& tm_out, const T* res, const CUtensorMap* tm_in_lo = nullptr,
+                       const CUtensorMap* tm_out_lo = nullptr) {
     lzb_pipe* p = c->pipe;
     const int Q = static_cast<int>(dc::cells_for(nb));
     if (p->pairs) {
@@ -430,12 +443,20 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
         cudaError_t le;
         {
             LaunchScope scope(c, kClassContraction);
-            auto kernel = p->aplanes == 2
-                              ? (nsplit > 1 ? dc2::conv_direct2_kernel<T, 2, true> : dc2::conv_direct2_kernel<T, 2, false>)
-                              : (nsplit > 1 ? dc2::conv_direct2_kernel<T, 1, true> : dc2::conv_direct2_kernel<T, 1, false>);
+            auto kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 1, true> : dc2::conv_direct2_kernel<T, 1, false>;
+            if (p->aplanes == 2) {
+                kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 2, true> : dc2::conv_direct2_kernel<T, 2, false>;
+            } else if (p->aplanes == 3) {
+                kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 3, true> : dc2::conv_direct2_kernel<T, 3, false>;
+            }
+            // the byte maps only matter to the e5m2 variant; any valid map serves the others
+            const CUtensorMap& in_lo = tm_in_lo ? *tm_in_lo : tm_in;
+            const CUtensorMap& w_lo = L.Wd8 ? L.tmW8[nsplit] : L.tmW2[nsplit];
+            const CUtensorMap& out_lo = tm_out_lo ? *tm_out_lo : tm_out;
             le = cudaLaunchKernelEx(&cfg, kernel, tm_in, L.tmW2[nsplit], tm_out, res,
                                     (const float*)L.mean, (const float*)L.invstd, Q, p->Cp,
-                                    kchunks, npairs, nsplit, c->d_err, L.achunks);
+                                    kchunks + L.lchunks, npairs, nsplit, c->d_err, L.achunks, in_lo, w_lo,
+                                    out_lo);
         }
         LZB_CUDA(le);
         LZB_CUDA(cudaGetLastError());
@@ -467,17 +488,25 @@ int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, fl
             in_dev, static_cast<T*>(c->IN), nb);
     }
     LZB_CUDA(cudaGetLastError());
-    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, c->tmXo, nullptr))) return rc;
+    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, c->tmXo, nullptr, nullptr, &c->tmXlo))) {
+        return rc;
+    }
     for (int b = 0; b < p->blocks; b++) {
-        if ((rc = launch_conv_direct<T>(c, p->layers[1 + 2 * b], nb, c->tmX, c->tmHo, nullptr))) return rc;
-        if ((rc = launch_conv_direct<T>(c, p->layers[2 + 2 * b], nb, c->tmH, c->tmXo, X))) return rc;
+        if ((rc = launch_conv_direct<T>(c, p->layers[1 + 2 * b], nb, c->tmX, c->tmHo, nullptr, &c->tmXl,
+                                        &c->tmHlo))) {
+            return rc;
+        }
+        if ((rc = launch_conv_direct<T>(c, p->layers[2 + 2 * b], nb, c->tmH, c->tmXo, X, &c->tmHl,
+                                        &c->tmXlo))) {
+            return rc;
+        }
     }
     const int cells = nb * kSq;
     {
         LaunchScope scope(c, kClassHead);
         dc::head_conv_cells_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(
-            X, p->head_w, p->Cp, cells, pol_dev, val_dev, p->Cp * p->aplanes,
-            p->aplanes == 2 ? p->Cp : 0);
+            X, p->head_w, p->Cp, cells, pol_dev, val_dev, p->row_bytes() / p->elt,
+            p->aplanes >= 2 ? p->Cp : 0, p->aplanes == 3 ? 1 : 0);
     }
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
@@ -535,6 +564,9 @@ int set_smem_attrs() {
         const void* variants[] = {
             (const void*)dc2::conv_direct2_kernel<__half, 1, false>, (const void*)dc2::conv_direct2_kernel<__half, 1, true>,
             (const void*)dc2::conv_direct2_kernel<__half, 2, false>, (const void*)dc2::conv_direct2_kernel<__half, 2, true>,
+            (const void*)dc2::conv_direct2_kernel<__half, 3, false>, (const void*)dc2::conv_direct2_kernel<__half, 3, true>,
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 3, false>,
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 3, true>,
             (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, false>,
             (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, true>,
             (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 2, false>,
@@ -724,6 +756,8 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
         if (p->wsplit) lo_mask = 1u << (wplanes - 1);
         L.cinw = L.cin_p * wplanes;
         L.achunks = L.cin_p * act_planes / 64;
+        // e5m2 low plane of the activations: 128 channels per chunk, none for the network input
+        L.lchunks = (p->aplanes == 3 && layer > 0) ? (L.cin_p + 127) / 128 : 0;
     }
     float* Wd32 = nullptr;           // fp32 filters in the implicit-GEMM layout (widened modes)
     if (rc == LZB_OK && p->direct && src_is_filters) {
@@ -731,7 +765,7 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
         const size_t n = (size_t)9 * p->Cp * L.cinw * p->elt;
         e = cudaMalloc(&L.Wd, n);
         if (e == cudaSuccess) e = cudaMemset(L.Wd, 0, n);
-        if (e == cudaSuccess && p->aplanes == 2) {
+        if (e == cudaSuccess && p->aplanes >= 2) {
             const size_t n32 = (size_t)9 * p->Cp * L.cin_p * sizeof(float);
             e = cudaMalloc(&Wd32, n32);
             if (e == cudaSuccess) e = cudaMemset(Wd32, 0, n32);
@@ -762,7 +796,7 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
             u_dev = U32;
         }
         if (rc == LZB_OK) {
-            if (p->direct && p->aplanes == 2) {
+            if (p->direct && p->aplanes >= 2) {
                 const size_t n32 = (size_t)9 * p->Cp * L.cin_p * sizeof(float);
                 e = cudaMalloc(&Wd32, n32);
                 if (e == cudaSuccess) e = cudaMemset(Wd32, 0, n32);
@@ -789,6 +823,14 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
         dc::widen_weights_kernel<__half><<<512, 256>>>(Wd32, static_cast<__half*>(L.Wd), L.cin_p, p->Cp,
                                                        wplanes, lo_mask);
         e = cudaGetLastError();
+        if (e == cudaSuccess && L.lchunks > 0) {
+            const int cin8 = L.lchunks * 128;
+            e = cudaMalloc(&L.Wd8, (size_t)9 * p->Cp * cin8);
+            if (e == cudaSuccess) {
+                dc::weights_to_e5m2_kernel<<<512, 256>>>(Wd32, L.Wd8, L.cin_p, cin8, p->Cp);
+                e = cudaGetLastError();
+            }
+        }
         if (e != cudaSuccess) rc = fail(LZB_ERR_CUDA, std::string("weight planes: ") + cudaGetErrorString(e));
     }
     if (rc == LZB_OK) {
@@ -808,6 +850,10 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
             if (p->Cp % ns != 0 || (p->Cp / ns) % 64 != 0) continue;
             rc = make_map_2d(&L.tmW2[ns], p->precision, L.Wd, (uint64_t)9 * p->Cp, L.cinw,
                              p->Cp / (2 * ns));
+            if (!rc && L.Wd8) {
+                rc = make_map_2d(&L.tmW8[ns], -1, L.Wd8, (uint64_t)9 * p->Cp, (uint64_t)L.lchunks * 128,
+                                 p->Cp / (2 * ns), 128);
+            }
             L.split_ok[ns] = (rc == LZB_OK);
         }
         if (rc) return rc;
@@ -860,7 +906,7 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
         case LZB_FP32: break;
         case LZB_FP16: case LZB_BF16: direct = true; break;
         case LZB_FP16_X2: case LZB_FP16_X3:
-            aplanes = 2;
+            aplanes = precision == LZB_FP16_X3 ? 2 : 3;
             wsplit = (precision == LZB_FP16_X3);
             precision = LZB_FP16;
             direct = true;
@@ -893,7 +939,7 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     p->wsplit = wsplit;
     // CTA pairs are the default; LZB_CONV_PAIRS=0 selects the one-CTA-per-tile
     // kernel (kept as a cross-check and for diagnostics).
-    p->pairs = direct && (aplanes == 2 ||
+    p->pairs = direct && (aplanes >= 2 ||
                           !(getenv("LZB_CONV_PAIRS") != nullptr && atoi(getenv("LZB_CONV_PAIRS")) == 0));
     p->elt = precision == LZB_FP32 ? 4 : 2;
     p->sm_count = prop.multiProcessorCount;
@@ -916,6 +962,7 @@ void lzb_pipe_destroy(lzb_pipe* p) {
     for (auto& L : p->layers) {
         cudaFree(L.U);
         cudaFree(L.Wd);
+        cudaFree(L.Wd8);
         cudaFree(L.mean);
         cudaFree(L.invstd);
     }
@@ -1029,8 +1076,8 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
         c->micro = c->micro_cap;
         c->Qa = round_up(static_cast<int>(dc::cells_for(c->micro_cap)), dc::kTileM);
         alloc(&c->IN, (size_t)c->Qa * 64 * p->elt);
-        alloc(&c->X, (size_t)c->Qa * p->Cp * p->aplanes * p->elt);
-        alloc(&c->H, (size_t)c->Qa * p->Cp * p->aplanes * p->elt);
+        alloc(&c->X, (size_t)c->Qa * p->row_bytes());
+        alloc(&c->H, (size_t)c->Qa * p->row_bytes());
     } else {
         c->micro = default_micro_batch(p, c->micro_cap);
         c->Pa = round_up(c->micro_cap * kTilesPerPos, 128);
@@ -1057,13 +1104,25 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
     *c->h_err = 0;
     if (p->direct) {
         int rc = make_map_2d(&c->tmIN, p->precision, c->IN, (uint64_t)c->Qa, 64, dc::kWinRows);
-        const uint64_t xp = (uint64_t)p->Cp * p->aplanes;     // channels of a cell row: hi [+ lo] plane
-        if (!rc) rc = make_map_2d(&c->tmX, p->precision, c->X, (uint64_t)c->Qa, xp, dc::kWinRows);
-        if (!rc) rc = make_map_2d(&c->tmH, p->precision, c->H, (uint64_t)c->Qa, xp, dc::kWinRows);
-        if (!rc) rc = make_map_2d(&c->tmXo, p->precision, c->X, (uint64_t)c->Qa, xp, 32, 32,
-                                  CU_TENSOR_MAP_SWIZZLE_64B);
-        if (!rc) rc = make_map_2d(&c->tmHo, p->precision, c->H, (uint64_t)c->Qa, xp, 32, 32,
-                                  CU_TENSOR_MAP_SWIZZLE_64B);
+        // 16-bit channels of a cell row (hi [+ 16-bit lo] plane) and the row pitch
+        const uint64_t xp = (uint64_t)p->Cp * (p->aplanes == 2 ? 2 : 1);
+        const uint64_t pitch = p->row_bytes();
+        const CUtensorMapSwizzle sw128 = CU_TENSOR_MAP_SWIZZLE_128B, sw64 = CU_TENSOR_MAP_SWIZZLE_64B;
+        if (!rc) rc = make_map_2d(&c->tmX, p->precision, c->X, (uint64_t)c->Qa, xp, dc::kWinRows, 64, sw128, pitch);
+        if (!rc) rc = make_map_2d(&c->tmH, p->precision, c->H, (uint64_t)c->Qa, xp, dc::kWinRows, 64, sw128, pitch);
+        if (!rc) rc = make_map_2d(&c->tmXo, p->precision, c->X, (uint64_t)c->Qa, xp, 32, 32, sw64, pitch);
+        if (!rc) rc = make_map_2d(&c->tmHo, p->precision, c->H, (uint64_t)c->Qa, xp, 32, 32, sw64, pitch);
+        if (p->aplanes == 3) {
+            // the e5m2 planes: Cp bytes per row, after the 16-bit channels
+            unsigned char* xl = static_cast<unsigned char*>(c->X) + 2 * p->Cp;
+            unsigned char* hl = static_cast<unsigned char*>(c->H) + 2 * p->Cp;
+            if (!rc) rc = make_map_2d(&c->tmXl, -1, xl, (uint64_t)c->Qa, p->Cp, dc::kWinRows, 128, sw128, pitch);
+            if (!rc) rc = make_map_2d(&c->tmHl, -1, hl, (uint64_t)c->Qa, p->Cp, dc::kWinRows, 128, sw128, pitch);
+            if (!rc) rc = make_map_2d(&c->tmXlo, -1, xl, (uint64_t)c->Qa, p->Cp, 32, 32,
+                                      CU_TENSOR_MAP_SWIZZLE_NONE, pitch);
+            if (!rc) rc = make_map_2d(&c->tmHlo, -1, hl, (uint64_t)c->Qa, p->Cp, 32, 32,
+                                      CU_TENSOR_MAP_SWIZZLE_NONE, pitch);
+        }
         if (rc) {
             lzb_ctx_destroy(c);
             return rc;
@@ -1400,7 +1459,7 @@ int lzb_ctx_debug_conv(lzb_ctx* c, int layer, const float* in, int n, const floa
     if (layer < 0 || layer >= (int)c->pipe->layers.size()) return fail(LZB_ERR_ARG, "layer out of range");
     if (!in || !out) return fail(LZB_ERR_ARG, "null buffer");
     LZB_CUDA(enter_device(c->pipe->device));
-    if (c->pipe->aplanes == 2) {
+    if (c->pipe->aplanes >= 2) {
         return fail(LZB_ERR_ARG, "single-layer diagnostics are not available in the two-plane modes");
     }
     if (c->pipe->direct) {
