@@ -18,7 +18,7 @@
 //
 //   engine_bench --weights FILE [--threads T] [--batch B] [--gpus G] [--visits V]
 //                [--moves M] [--games N] [--batching eager|wait]
-//                [--precision fp16|bf16|fp32] [--verbose]
+//                [--precision fp16|fp16x2|bf16|fp32] [--verbose]
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -98,7 +98,8 @@ int main(int argc, char** argv) {
         else if (k == "--batching") lzb_engine::eager = (v == "eager");
         else if (k == "--precision") {
             lzb_engine::precision = v == "fp32" ? CUDAPipe::Precision::FP32
-                                  : v == "bf16" ? CUDAPipe::Precision::BF16 : CUDAPipe::Precision::FP16;
+                                  : v == "bf16" ? CUDAPipe::Precision::BF16
+                                  : v == "fp16x2" ? CUDAPipe::Precision::FP16_X2 : CUDAPipe::Precision::FP16;
         } else { std::fprintf(stderr, "unknown option %s\n", k.c_str()); return 2; }
     }
     if (weights.empty()) { std::fprintf(stderr, "--weights is required\n"); return 2; }
