@@ -237,6 +237,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-strict-mode", action="store_true",
+                    help="skip the extra timing of the fp16x2 mode")
     ap.add_argument("--precision", default=PRECISION,
                     choices=["fp16", "bf16", "fp16-winograd", "bf16-winograd", "fp32", "fp16x2", "fp16x3"])
     args = ap.parse_args()
@@ -377,6 +379,22 @@ def main():
             "kernel_time_share": {k: (v[0] / total_ms if total_ms else 0.0) for k, v in prof.items()},
             "kernel_ms_per_step": {k: v[0] / prof_steps for k, v in prof.items()},
         }
+        if world == 1 and args.precision == "fp16" and not args.no_strict_mode:
+            # The same workload in the mode that holds the half-precision accuracy
+            # bounds for every position of this 40-block network (activations as
+            # fp16 + e5m2): a second figure beside the headline, device-resident.
+            ctx.close()
+            pipe.close()
+            pipe = pkg.Pipe(net, "fp16x2", device=local)
+            ctx = pipe.context(B)
+            stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+            ms_strict, _ = timed(step_device, args.steps, args.warmup)
+            out["strict_accuracy_mode"] = {
+                "precision": "fp16x2", "value": whole_job_rate(B, world, ms_strict), "unit": "positions/s",
+                "ms_per_step": ms_strict,
+                "note": "policy <= 2e-3 and winrate <= 5e-3 against the reference for every position "
+                        "(tests/test_gpu_parity.py::test_config3_40x256_batch256); the headline mode "
+                        "holds the winrate bound for 95 % of positions"}
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             sys.path.insert(0, os.path.join(ROOT, "oracle"))
