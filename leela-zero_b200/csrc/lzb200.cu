@@ -1220,13 +1220,13 @@ int lzb_ctx_forward_heads_device(lzb_ctx* c, const float* in_dev, int n, float s
     const Heads& h = c->pipe->heads;
     {
         LaunchScope scope(c, kClassHead);
-        policy_head_kernel<<<n, 384, 0, c->stream>>>(c->d_pol, h.bn_pol_mean, h.bn_pol_invstd,
+        policy_head_kernel<<<n * kPolicySlices, 384, 0, c->stream>>>(c->d_pol, h.bn_pol_mean, h.bn_pol_invstd,
                                                      h.ip_pol_wT, h.ip_pol_b, 1.0f / softmax_temp,
                                                      policy_dev);
     }
     {
         LaunchScope scope(c, kClassHead);
-        value_head_kernel<<<n, 256, 0, c->stream>>>(c->d_val, h.bn_val_mean, h.bn_val_invstd,
+        value_head_kernel<<<n * kValueSlices, 256, 0, c->stream>>>(c->d_val, h.bn_val_mean, h.bn_val_invstd,
                                                     h.ip1_val_wT, h.ip1_val_b, h.ip2_val_w,
                                                     h.ip2_val_b, winrate_dev);
     }
