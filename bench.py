@@ -43,7 +43,7 @@ FLOPS_GEMM_PER_POS = 2 * 36 * 25 * FILTERS * FILTERS
 # algorithmic FLOPs of one 3x3 layer per position as a direct convolution (C = K = 256)
 FLOPS_CONV_PER_POS = 2 * 9 * FILTERS * FILTERS * 361
 # DRAM traffic (read + write) of one conv_direct_kernel launch at 256 positions, from the committed ncu capture
-GEMM_DRAM_BYTES_PER_LAUNCH = 90.1e6   # mean of two captured launches (66 and 113 MB), profiles/conv_direct2_kernel_40x256_batch256.md
+GEMM_DRAM_BYTES_PER_LAUNCH = 90.1e6   # mean of two captured launches (66 and 113 MB)
 
 
 def load_package():

@@ -44,13 +44,18 @@ extern "C" {
  *                      pipeline (transform, 36 batched contractions, fused
  *                      output/input transform).  3.6x fewer multiply-adds, about
  *                      4x the rounding error of the direct form.
- *  LZB_FP16_X2         the direct convolution with every activation carried as
+ *  LZB_FP16_X2         the direct convolution with activations carried as
  *                      x = hi + lo, hi in fp16 and lo in e5m2 (one byte); the
  *                      fp16 plane is multiplied with the fp16 weights, the e5m2
  *                      plane with an e5m2 copy of them (kind::f8f6f4 MMAs, half
- *                      the time of the fp16 ones): 1.6x the cost of LZB_FP16.
- *                      Removes the rounding of the activations, which is what
- *                      limits LZB_FP16 on deep networks; holds the
+ *                      the time of the fp16 ones): 1.5x the cost of LZB_FP16
+ *                      for a layer that carries the plane.  Removes the
+ *                      rounding of the activations, which is what limits
+ *                      LZB_FP16 on deep networks.  Rounding errors made in the
+ *                      first blocks are the ones the rest of the tower
+ *                      amplifies, so by default only the first half of a tower
+ *                      deeper than 24 blocks carries the low plane
+ *                      (lzb_pipe_set_low_plane_blocks); holds the
  *                      half-precision bounds (policy 2e-3, winrate 5e-3) for
  *                      every position at 40 blocks.
  *  LZB_FP16_X3         activations and weights both carried as two fp16 planes
@@ -93,6 +98,17 @@ int lzb_device_count(int* count);
 int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks,
                     int precision);
 void lzb_pipe_destroy(lzb_pipe* p);
+
+/*
+ * LZB_FP16_X2 pipes only, before the first layer is pushed: carry the e5m2
+ * low plane of the activations through the first `n` residual blocks (and the
+ * input convolution) and run the blocks after them on the fp16 plane alone.
+ * n < 0 or n > blocks: every block.  The default is every block for towers of
+ * up to 24 blocks and the first half of deeper ones (see LZB_FP16_X2 above).
+ * Precision selection has no finer grain in the reference
+ * (cfg_precision, src/Network.cpp:417-493); this knob has no counterpart there.
+ */
+int lzb_pipe_set_low_plane_blocks(lzb_pipe* p, int n);
 
 /*
  * Upload one 3x3 convolution layer.  `layer` 0 is the input convolution

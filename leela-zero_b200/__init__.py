@@ -31,6 +31,7 @@ SYMBOLS = (
     "lzb_ctx_debug_conv", "lzb_ctx_profile_begin", "lzb_ctx_profile_end",
     "lzb_conv3x3_static", "lzb_ctx_debug_wait_probe", "lzb_host_alloc", "lzb_host_free",
     "lzb_pipe_push_conv_filters", "lzb_ctx_forward_packed", "lzb_ctx_forward_heads_packed",
+    "lzb_pipe_set_low_plane_blocks",
 )
 
 _f32p = ctypes.POINTER(ctypes.c_float)
@@ -56,6 +57,7 @@ def lib():
         vp = ctypes.c_void_p
         L.lzb_pipe_create.argtypes = [ctypes.POINTER(vp)] + [ctypes.c_int] * 4
         L.lzb_pipe_destroy.argtypes = [vp]
+        L.lzb_pipe_set_low_plane_blocks.argtypes = [vp, ctypes.c_int]
         L.lzb_pipe_push_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
         L.lzb_pipe_push_head_convs.argtypes = [vp, _f32p, _f32p]
         L.lzb_pipe_push_heads.argtypes = [vp] + [_f32p] * 10
@@ -119,17 +121,21 @@ class Pipe:
     ``push_weights`` (src/ForwardPipe.h:40-54): ``U`` (list of fp32
     ``[36][c_in][C]``), ``bn_mean``, ``bn_invstd`` (lists of ``[C]``),
     ``pol_w`` ``[2][C]``, ``val_w`` ``[1][C]``, plus optionally ``heads``.
-    With ``from_filters`` the layers come from ``net["filters"]`` (untransformed
+    ``low_plane_blocks`` (``"fp16x2"`` only) overrides how many residual blocks carry
+    the e5m2 plane of the activations.  With ``from_filters`` the layers come from ``net["filters"]`` (untransformed
     ``[C][c_in][3][3]``, as ``weights.load_network`` returns them) instead of ``U``.
     """
 
-    def __init__(self, net, precision="fp16", device=0, heads=True, from_filters=False):
+    def __init__(self, net, precision="fp16", device=0, heads=True, from_filters=False,
+                 low_plane_blocks=None):
         L = lib()
         self.h = ctypes.c_void_p()
         self.channels, self.blocks = net["channels"], net["blocks"]
         self.precision = PRECISIONS[precision] if isinstance(precision, str) else precision
         check(L.lzb_pipe_create(ctypes.byref(self.h), device, self.channels, self.blocks,
                                 self.precision))
+        if low_plane_blocks is not None:     # fp16x2: blocks that carry the e5m2 plane (-1 = all)
+            check(L.lzb_pipe_set_low_plane_blocks(self.h, low_plane_blocks))
         for l in range(len(net["bn_mean"])):
             mean = _ptr(np.ascontiguousarray(net["bn_mean"][l], np.float32))
             inv = _ptr(np.ascontiguousarray(net["bn_invstd"][l], np.float32))

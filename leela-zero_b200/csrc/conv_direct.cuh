@@ -255,12 +255,6 @@ __device__ __forceinline__ void epilogue_chunk_e5m2(const uint32_t (&r)[32], con
         *reinterpret_cast<uint4*>(stg_row + ((v ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
-// The 32 x 32-byte e5m2 tile of a warp in its staging buffer, rows unswizzled.
-__device__ __forceinline__ void stage_e5m2_plane(const uint32_t (&lo)[8], unsigned char* stg, int lane) {
-    uint4* row = reinterpret_cast<uint4*>(stg + lane * 32);
-    row[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    row[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
-}
 
 // Hand the warp's staging tile to the TMA engine: rows m .. m+31, channels
 // col .. col+31 of the output.  Every lane fences its shared-memory writes

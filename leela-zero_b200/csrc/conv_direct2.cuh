@@ -126,8 +126,12 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
 // [Kp, 2 Kp) of tmO and res, see epilogue_chunk_x2), or 3 when the low plane is
 // e5m2: a cell row is [Kp x 16 bits | Kp bytes]; chunks c >= achunks then come
 // from tmXl / tmWl (byte maps, 128 channels per 128-byte chunk) and are
-// multiplied by kind::f8f6f4 MMAs, and the low output plane goes out through
-// tmOl (bytes, box 32 x 32).  tmXl, tmWl, tmOl are ignored otherwise.
+// multiplied by kind::f8f6f4 MMAs, and the low output plane (out_lo: its first
+// byte, out_pitch bytes per cell row, rows below q_rows exist) is written with
+// plain 32-byte stores, one sector per cell and chunk, straight from the
+// registers.  tmXl, tmWl, out_lo are ignored otherwise.
+// ldr : elements of T per cell row of the residual tensor (its rows may be
+// wider than Kp when the tensor also holds a low plane).
 //
 // The kernel is launched with programmatic stream serialization: it lets its
 // successor start at once (griddepcontrol.launch_dependents) and itself waits
@@ -140,7 +144,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     const __grid_constant__ CUtensorMap tmO, const T* res, const float* __restrict__ bn_mean,
     const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int npairs, int nsplit,
     int* err, int achunks, const __grid_constant__ CUtensorMap tmXl,
-    const __grid_constant__ CUtensorMap tmWl, const __grid_constant__ CUtensorMap tmOl) {
+    const __grid_constant__ CUtensorMap tmWl, int ldr, unsigned char* out_lo, int out_pitch,
+    int q_rows) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -346,8 +351,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             const bool use_res = (res != nullptr) && interior;
             constexpr bool two = kPlanes == 2;
             constexpr bool e5 = kPlanes == 3;
-            // elements of T per cell row of the residual tensor
-            const int ldr = two ? 2 * Kp : (e5 ? Kp + (Kp >> 1) : Kp);
             const T* rrow = res + static_cast<size_t>(q) * ldr + col0;
             // e5m2 plane of the same row: Kp bytes after the Kp 16-bit channels
             const unsigned char* erow =
@@ -366,9 +369,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                     epilogue_chunk_e5m2<T>(r, v, e, s_scale + col, s_bias + col, use_res, interior, stg_row,
                                            lane, lo);
                     store_staged_tile(&tmO, stg, col, row0, lane);
-                    wait_staged_tile_read(lane);
-                    stage_e5m2_plane(lo, stg_ptr, lane);
-                    store_staged_tile(&tmOl, stg, col, row0, lane);
+                    if (q < q_rows) {
+                        uint4* dst = reinterpret_cast<uint4*>(out_lo + static_cast<size_t>(q) * out_pitch + col);
+                        dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        dst[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                    }
                 } else if constexpr (!two) {
                     epilogue_chunk<T>(r, v, s_scale + col, s_bias + col, use_res, interior, stg_row, lane);
                     store_staged_tile(&tmO, stg, col, row0, lane);

@@ -126,6 +126,7 @@ struct Layer {
     int achunks = 0;            // 64-channel chunks of the activation tensor this layer reads
     unsigned char* Wd8 = nullptr;   // e5m2 copy of the weights [9][Kp][cin8] (LZB_FP16_X2), or null
     int lchunks = 0;            // 128-channel e5m2 chunks that follow the fp16 chunks
+    bool out_lo = false;        // this layer writes an e5m2 low plane beside its fp16 output
     CUtensorMap tmW8[5];        // byte maps over Wd8, box 128 x Kp/(2*ns)
     CUtensorMap tmW;            // box 64 x Kp   (one CTA per tile)
     CUtensorMap tmW2[5];        // CTA pairs: [ns] has box 64 x Kp/(2*ns), ns = 1..4 where valid
@@ -153,6 +154,10 @@ struct lzb_pipe {
                                 // 3 = a 16-bit plane and an e5m2 plane (LZB_FP16_X2)
     // bytes of one cell row of the activation tensors
     int row_bytes() const { return aplanes == 3 ? 3 * Cp : aplanes * Cp * elt; }
+    // LZB_FP16_X2: layers 0 .. lo_layers-1 write the e5m2 plane and layers
+    // 1 .. lo_layers-1 read it; the layers after them run on the fp16 plane alone
+    // (same buffers, the low bytes of a row are then neither written nor read).
+    int lo_layers = 0;
     bool wsplit = false;        // weights carried as hi + lo planes as well (LZB_FP16_X3)
     int elt = 2;        // bytes per stored element
     int sm_count = 0;
@@ -187,7 +192,6 @@ struct lzb_ctx {
     CUtensorMap tmIN, tmX, tmH;      // window loads
     CUtensorMap tmXo, tmHo;          // 32 x 32 output stores
     CUtensorMap tmXl, tmHl;          // e5m2 planes of X and H: 128-byte windows (LZB_FP16_X2)
-    CUtensorMap tmXlo, tmHlo;        // ... and their 32 x 32-byte output stores
     long long launches = 0;
     // per-launch timing (diagnostics): event pairs tagged with a kernel class
     bool profiling = false;
@@ -379,7 +383,7 @@ int run_tower(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* va
 template <typename T>
 int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm_in,
                        const CUtensorMap& tm_out, const T* res, const CUtensorMap* tm_in_lo = nullptr,
-                       const CUtensorMap* tm_out_lo = nullptr) {
+                       void* out = nullptr) {
     lzb_pipe* p = c->pipe;
     const int Q = static_cast<int>(dc::cells_for(nb));
     if (p->pairs) {
@@ -446,17 +450,19 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
             auto kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 1, true> : dc2::conv_direct2_kernel<T, 1, false>;
             if (p->aplanes == 2) {
                 kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 2, true> : dc2::conv_direct2_kernel<T, 2, false>;
-            } else if (p->aplanes == 3) {
+            } else if (L.out_lo || L.lchunks > 0) {
                 kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 3, true> : dc2::conv_direct2_kernel<T, 3, false>;
             }
             // the byte maps only matter to the e5m2 variant; any valid map serves the others
             const CUtensorMap& in_lo = tm_in_lo ? *tm_in_lo : tm_in;
             const CUtensorMap& w_lo = L.Wd8 ? L.tmW8[nsplit] : L.tmW2[nsplit];
-            const CUtensorMap& out_lo = tm_out_lo ? *tm_out_lo : tm_out;
+            const int ldr = p->row_bytes() / p->elt;
+            unsigned char* out_lo =
+                (L.out_lo && out) ? static_cast<unsigned char*>(out) + (size_t)p->Cp * p->elt : nullptr;
             le = cudaLaunchKernelEx(&cfg, kernel, tm_in, L.tmW2[nsplit], tm_out, res,
                                     (const float*)L.mean, (const float*)L.invstd, Q, p->Cp,
                                     kchunks + L.lchunks, npairs, nsplit, c->d_err, L.achunks, in_lo, w_lo,
-                                    out_lo);
+                                    ldr, out_lo, p->row_bytes(), c->Qa);
         }
         LZB_CUDA(le);
         LZB_CUDA(cudaGetLastError());
@@ -488,16 +494,16 @@ int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, fl
             in_dev, static_cast<T*>(c->IN), nb);
     }
     LZB_CUDA(cudaGetLastError());
-    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, c->tmXo, nullptr, nullptr, &c->tmXlo))) {
+    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, c->tmXo, nullptr, nullptr, c->X))) {
         return rc;
     }
     for (int b = 0; b < p->blocks; b++) {
         if ((rc = launch_conv_direct<T>(c, p->layers[1 + 2 * b], nb, c->tmX, c->tmHo, nullptr, &c->tmXl,
-                                        &c->tmHlo))) {
+                                        c->H))) {
             return rc;
         }
         if ((rc = launch_conv_direct<T>(c, p->layers[2 + 2 * b], nb, c->tmH, c->tmXo, X, &c->tmHl,
-                                        &c->tmXlo))) {
+                                        c->X))) {
             return rc;
         }
     }
@@ -506,7 +512,8 @@ int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, fl
         LaunchScope scope(c, kClassHead);
         dc::head_conv_cells_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(
             X, p->head_w, p->Cp, cells, pol_dev, val_dev, p->row_bytes() / p->elt,
-            p->aplanes >= 2 ? p->Cp : 0, p->aplanes == 3 ? 1 : 0);
+            (p->aplanes == 2 || (p->aplanes == 3 && p->layers.back().out_lo)) ? p->Cp : 0,
+            p->aplanes == 3 ? 1 : 0);
     }
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
@@ -756,8 +763,10 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
         if (p->wsplit) lo_mask = 1u << (wplanes - 1);
         L.cinw = L.cin_p * wplanes;
         L.achunks = L.cin_p * act_planes / 64;
-        // e5m2 low plane of the activations: 128 channels per chunk, none for the network input
-        L.lchunks = (p->aplanes == 3 && layer > 0) ? (L.cin_p + 127) / 128 : 0;
+        // e5m2 low plane of the activations: 128 channels per chunk, none for the network
+        // input and none beyond the layers that carry the plane
+        L.lchunks = (p->aplanes == 3 && layer > 0 && layer < p->lo_layers) ? (L.cin_p + 127) / 128 : 0;
+        L.out_lo = p->aplanes == 3 && layer < p->lo_layers;
     }
     float* Wd32 = nullptr;           // fp32 filters in the implicit-GEMM layout (widened modes)
     if (rc == LZB_OK && p->direct && src_is_filters) {
@@ -870,6 +879,23 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
 // C ABI
 // ===========================================================================
 
+namespace {
+// LZB_FP16_X2: how many residual blocks, counted from the input, carry the e5m2
+// low plane by default.  A rounding error made in block b is amplified by the
+// blocks after it, and most by the early ones, where the residual stream is
+// still small next to what a block adds to it: in a 40-block network the low
+// plane stops changing the final error somewhere between block 16 and 20, so
+// the first half of a deep tower carries it and shallow towers carry it
+// throughout.
+int default_low_plane_blocks(int blocks) {
+    if (const char* e = getenv("LZB_X2_BLOCKS")) {
+        const int n = atoi(e);
+        return (n < 0 || n > blocks) ? blocks : n;
+    }
+    return blocks <= 24 ? blocks : (blocks + 1) / 2;
+}
+}  // namespace
+
 extern "C" {
 
 const char* lzb_last_error(void) { return g_error.c_str(); }
@@ -937,6 +963,7 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     p->direct = direct;
     p->aplanes = aplanes;
     p->wsplit = wsplit;
+    if (aplanes == 3) p->lo_layers = 1 + 2 * default_low_plane_blocks(blocks);
     // CTA pairs are the default; LZB_CONV_PAIRS=0 selects the one-CTA-per-tile
     // kernel (kept as a cross-check and for diagnostics).
     p->pairs = direct && (aplanes >= 2 ||
@@ -953,6 +980,17 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     }
     p->layers.resize(1 + 2 * blocks);
     *out = p;
+    return LZB_OK;
+}
+
+int lzb_pipe_set_low_plane_blocks(lzb_pipe* p, int n) {
+    if (!p) return fail(LZB_ERR_ARG, "null pipe");
+    if (p->aplanes != 3) return fail(LZB_ERR_ARG, "only LZB_FP16_X2 pipes carry a low plane");
+    for (const Layer& L : p->layers) {
+        if (L.present) return fail(LZB_ERR_ARG, "set the low-plane blocks before the first layer is pushed");
+    }
+    if (n < 0 || n > p->blocks) n = p->blocks;
+    p->lo_layers = 1 + 2 * n;
     return LZB_OK;
 }
 
@@ -1118,10 +1156,6 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
             unsigned char* hl = static_cast<unsigned char*>(c->H) + 2 * p->Cp;
             if (!rc) rc = make_map_2d(&c->tmXl, -1, xl, (uint64_t)c->Qa, p->Cp, dc::kWinRows, 128, sw128, pitch);
             if (!rc) rc = make_map_2d(&c->tmHl, -1, hl, (uint64_t)c->Qa, p->Cp, dc::kWinRows, 128, sw128, pitch);
-            if (!rc) rc = make_map_2d(&c->tmXlo, -1, xl, (uint64_t)c->Qa, p->Cp, 32, 32,
-                                      CU_TENSOR_MAP_SWIZZLE_NONE, pitch);
-            if (!rc) rc = make_map_2d(&c->tmHlo, -1, hl, (uint64_t)c->Qa, p->Cp, 32, 32,
-                                      CU_TENSOR_MAP_SWIZZLE_NONE, pitch);
         }
         if (rc) {
             lzb_ctx_destroy(c);

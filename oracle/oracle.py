@@ -31,9 +31,15 @@ def _ptr(a):
     return a.ctypes.data_as(_f32p)
 
 
-def build(ref_root="/root/reference"):
+def reference_root():
+    """Where the leela-zero source tree lies: the LZ_REFERENCE environment
+    variable, else the place this build environment mounts it."""
+    return os.environ.get("LZ_REFERENCE", "/root/reference")
+
+
+def build(ref_root=None):
     """Compile the checker libraries with the Makefile beside this file."""
-    subprocess.run(["make", "-C", HERE, "REF=" + ref_root], check=True,
+    subprocess.run(["make", "-C", HERE, "REF=" + (ref_root or reference_root())], check=True,
                    stdout=subprocess.DEVNULL)
 
 

@@ -13,6 +13,12 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu)")
 
 
+def reference_root():
+    """The leela-zero source tree (present in the build container only)."""
+    import oracle as O
+    return O.reference_root()
+
+
 def load_package():
     """Import the package directory ``leela-zero_b200`` (not a valid module
     name, hence by path) as ``leela_zero_b200``."""

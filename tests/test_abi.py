@@ -41,6 +41,6 @@ def test_product_does_not_touch_the_oracle():
     pkg = os.path.join(ROOT, "leela-zero_b200")
     for base, _, files in os.walk(pkg):
         for f in files:
-            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h", ".hpp", ".mk")) or f == "Makefile":
                 text = open(os.path.join(base, f), errors="ignore").read()
                 assert "oracle" not in text.lower(), os.path.join(base, f)

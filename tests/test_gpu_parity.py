@@ -7,8 +7,11 @@ Tolerances (max-abs after the heads, i.e. on policy[362] and winrate):
   fp16 / bf16 operand modes policy <= 2e-3, winrate <= 5e-3
 and the engine's self-check distance (src/Network.cpp:667-690) <= 0.2.
 
-Where a 16-bit mode cannot meet the max-abs bound the test says so and states
-the bound it does hold (see `test_config2_...` and `test_config3_...`).
+"fp16x2" (fp16 activations with an e5m2 correction plane) is the mode the
+benchmark is quoted on and the one held to these bounds as max-abs over every
+position of every configuration.  Plain "fp16" is the fast mode: it misses the
+winrate bound on a few per cent of the positions of deep networks, and the
+tests that touch it say which bound they characterise it by.
 """
 import threading
 
@@ -151,28 +154,34 @@ def test_config1_batch8(lzb, oracle, W):
         assert l2 <= SELFCHECK_MAX and ew.max() <= wtol and ep.max() <= 5e-2, mode
     cal = W.synthetic_network(10, 128, 2011, calibrated=True)
     _, _, rp, rw = _reference(oracle, cal, x)
-    policy, win = lzb.Pipe(cal, "fp16").context(8).forward_heads(x)
-    ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
-    assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16 and l2 <= SELFCHECK_MAX
+    for mode in ("fp16x2", "fp16"):
+        policy, win = lzb.Pipe(cal, mode).context(8).forward_heads(x)
+        ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
+        assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16 and l2 <= SELFCHECK_MAX, mode
 
 
 @pytest.mark.parametrize("n", [1, 8, 32, 128])
 def test_config2_20x256_batch_sweep(lzb, oracle, W, n):
     """20 blocks x 256 filters (BN-calibrated random init), batch 1/8/32/128.
 
-    fp32: 1e-4.  fp16: policy within 2e-3 at every batch size.  The winrate
-    bound of 5e-3 holds for at least 95 % of the positions; its maximum over
-    128 positions is about 6e-3, which is the rounding floor of fp16 operands
-    themselves (an exact-accumulation emulation of direct fp16 convolution
-    gives 6.5e-3 over 96 positions), so the maximum is held to 1e-2.  bf16 has
-    3 fewer mantissa bits (8x coarser) and is held to the engine's self-check only."""
+    fp32: 1e-4.  fp16x2, the benchmarked mode: policy 2e-3 and winrate 5e-3 as
+    max-abs over every position, at every batch size (small batches take other
+    kernels than large ones).  The fast mode fp16 is characterised, not held to
+    the bound: policy within 2e-3; winrate within 5e-3 for at least 95 % of the
+    positions and within 1e-2 for all (its maximum over 128 positions is about
+    6e-3, the rounding floor of fp16 operands: an exact-accumulation emulation
+    gives 6.5e-3 over 96 positions).  bf16 has 3 fewer mantissa bits (8x
+    coarser) and is held to the engine's self-check only."""
     net = W.synthetic_network(20, 256, 2003, calibrated=True)
     x = W.synthetic_positions(n, 1020)
     _, _, rp, rw = _reference(oracle, net, x)
     policy, win = lzb.Pipe(net, "fp32").context(n).forward_heads(x)
     ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
     assert ep.max() <= TOL_FP32 and ew.max() <= TOL_FP32
-    policy, win = lzb.Pipe(net, "fp16").context(n).forward_heads(x)
+    policy, win = lzb.Pipe(net, "fp16x2").context(n).forward_heads(x)
+    ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
+    assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16 and l2 <= SELFCHECK_MAX
+    policy, win = lzb.Pipe(net, "fp16").context(n).forward_heads(x)     # fast mode, characterised
     ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
     assert ep.max() <= TOL_POLICY_16
     assert np.percentile(ew, 95) <= TOL_VALUE_16 and ew.max() <= 1e-2
@@ -185,11 +194,19 @@ def test_config2_20x256_batch_sweep(lzb, oracle, W, n):
 
 def test_config3_40x256_batch256(lzb, oracle, W):
     """The headline configuration: 40 blocks x 256 filters, 256 positions,
-    exactly the network and precision bench.py times.  Same bounds as config 2."""
+    exactly the network and precision (fp16x2, its default low-plane schedule)
+    bench.py times: policy 2e-3 and winrate 5e-3 as max-abs over all 256
+    positions.  The same with the low plane on every block must hold them too;
+    the fast mode fp16 is characterised as in config 2."""
     net = W.synthetic_network(40, 256, 2003, calibrated=True)
     x = W.synthetic_positions(256, 1040)
     _, _, rp, rw = _reference(oracle, net, x)
-    policy, win = lzb.Pipe(net, "fp16").context(256).forward_heads(x)
+    for blocks_with_low_plane in (None, -1):
+        policy, win = lzb.Pipe(net, "fp16x2", low_plane_blocks=blocks_with_low_plane).context(256).forward_heads(x)
+        ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
+        print("fp16x2 low-plane blocks %s: policy %.3g winrate %.3g" % (blocks_with_low_plane, ep.max(), ew.max()))
+        assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16 and l2 <= SELFCHECK_MAX
+    policy, win = lzb.Pipe(net, "fp16").context(256).forward_heads(x)       # fast mode, characterised
     ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
     assert ep.max() <= TOL_POLICY_16
     assert np.percentile(ew, 95) <= TOL_VALUE_16 and ew.max() <= 1e-2
@@ -197,11 +214,6 @@ def test_config3_40x256_batch256(lzb, oracle, W):
     policy, win = lzb.Pipe(net, "fp32").context(256).forward_heads(x[:16])
     ep, ew, l2 = _errors(oracle, policy, win, rp[:16], rw[:16])
     assert ep.max() <= TOL_FP32 and ew.max() <= TOL_FP32
-    # activations carried as hi + lo fp16 planes: the half-precision bounds hold
-    # for EVERY position at this depth (twice the MMAs of "fp16")
-    policy, win = lzb.Pipe(net, "fp16x2").context(256).forward_heads(x)
-    ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
-    assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16 and l2 <= SELFCHECK_MAX
     # weights as hi + lo too: an order of magnitude closer than "fp16"
     policy, win = lzb.Pipe(net, "fp16x3").context(64).forward_heads(x[:64])
     ep, ew, l2 = _errors(oracle, policy, win, rp[:64], rw[:64])

@@ -6,7 +6,7 @@ import os
 import numpy as np
 import pytest
 
-from conftest import ROOT, load_package
+from conftest import ROOT, load_package, reference_root as _reference_root
 
 GOLDEN = os.path.join(ROOT, "tests", "golden", "cpupipe_golden.npz")
 
@@ -161,7 +161,7 @@ def test_v1_file_rejects_bad_files(W, tmp_path):
 def test_reference_fixture_file_parses(W):
     """src/tests/0k.txt, the only network file in the reference tree: 27 lines
     -> 1 block x 8 filters (src/Network.cpp:243-259)."""
-    path = "/root/reference/src/tests/0k.txt"
+    path = os.path.join(_reference_root(), "src", "tests", "0k.txt")
     if not os.path.exists(path):
         pytest.skip("reference tree not present")
     raw = W.read_v1(path)
@@ -171,7 +171,7 @@ def test_reference_fixture_file_parses(W):
 
 
 def test_reference_fixture_file_runs_through_the_oracle(oracle, W):
-    path = "/root/reference/src/tests/0k.txt"
+    path = os.path.join(_reference_root(), "src", "tests", "0k.txt")
     if not os.path.exists(path) or not oracle.ref_available():
         pytest.skip("reference tree not present")
     net = W.prepare(W.read_v1(path))

@@ -9,7 +9,7 @@ import subprocess
 import numpy as np
 import pytest
 
-from conftest import ROOT
+from conftest import ROOT, reference_root
 
 HOST = os.path.join(ROOT, "leela-zero_b200", "host")
 CPP = os.path.join(ROOT, "tests", "cpp")
@@ -49,7 +49,7 @@ def test_scheduler_under_thread_sanitizer(tmp_path, lzb):
 def test_cudapipe_builds_against_the_reference_headers(tmp_path):
     """With LZ_REFERENCE_TREE the class derives from the engine's own
     ForwardPipe (drop-in check; only where the reference tree is present)."""
-    ref = "/root/reference/src"
+    ref = os.path.join(reference_root(), "src")
     if not os.path.exists(os.path.join(ref, "ForwardPipe.h")):
         pytest.skip("reference tree not present")
     out = str(tmp_path / "CUDAPipe.o")
