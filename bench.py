@@ -3,14 +3,20 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (config 3): 40 residual blocks x 256 filters, fp16 operands with fp32
-accumulation, 256 positions per GPU per step, random-init weights and
-synthetic positions.  A step is one complete evaluation of a batch: tower, 1x1
-head convolutions and the policy/value heads.
+Workload (config 3): 40 residual blocks x 256 filters, 256 positions per GPU per
+step, random-init weights and synthetic positions, in the mode that holds the
+half-precision accuracy bounds against the reference for every position
+("fp16x2": fp16 operands plus e5m2 correction planes in the first blocks, fp32
+accumulation).  A step is one complete evaluation of a batch: tower, 1x1 head
+convolutions and the policy/value heads.
 
 Prints ONE JSON line.  `value` is positions/second with the inputs already in
 HBM; `e2e` is the same metric through the host-buffer entry point of the C ABI
-(pinned host memory, copies inside the timed region).  With N > 1 the script is
+(bit-packed positions in pinned host memory, results read back to pinned host
+memory, copies inside the timed region, two contexts driven by two host
+threads the way the scheduler's workers drive a GPU).  `fast_mode` is the same
+workload in plain fp16, which is faster and misses the winrate bound on a few
+per cent of the positions.  With N > 1 the script is
 launched by torch.distributed.run, one rank per GPU; positions are sharded, the
 path has no collective, so the process group only serves the barrier and the
 max-over-ranks of the device times.
@@ -34,7 +40,8 @@ BLOCKS, FILTERS, BATCH = 40, 256, 256
 WEIGHT_SEED, INPUT_SEED = 2003, 1003
 WORKLOAD = ("config 3: 40 blocks x 256 filters, %d positions per GPU per step, "
             "tower + 1x1 head convs + policy/value heads")
-PRECISION = "fp16"
+PRECISION = "fp16x2"
+FAST_PRECISION = "fp16"
 # direct-convolution FLOPs per position, tower + 1x1 convs + the three FC layers
 FLOPS_DIRECT = (2 * 9 * 18 * FILTERS * 361 + 2 * BLOCKS * 2 * 9 * FILTERS * FILTERS * 361
                 + 2 * FILTERS * 3 * 361 + 708072)
@@ -43,7 +50,7 @@ FLOPS_GEMM_PER_POS = 2 * 36 * 25 * FILTERS * FILTERS
 # algorithmic FLOPs of one 3x3 layer per position as a direct convolution (C = K = 256)
 FLOPS_CONV_PER_POS = 2 * 9 * FILTERS * FILTERS * 361
 # DRAM traffic (read + write) of one conv_direct_kernel launch at 256 positions, from the committed ncu capture
-GEMM_DRAM_BYTES_PER_LAUNCH = 90.1e6   # mean of two captured launches (66 and 113 MB)
+GEMM_DRAM_BYTES_PER_LAUNCH = {"fp16": 90.1e6}   # per mode; fp16: mean of two captured launches (66 and 113 MB)
 
 
 def load_package():
@@ -228,6 +235,37 @@ def default_micro_batch(precision, B):
     return min(n, B)
 
 
+def config2_sweep(pkg, W, torch, dev, device_index, precision):
+    """Config 2: 20 blocks x 256 filters at batch 1 / 8 / 32 / 128, device-resident,
+    complete evaluations, CUDA events on the context's stream around 20 steps each."""
+    net = W.synthetic_network(20, FILTERS, WEIGHT_SEED, calibrated=True)
+    pipe = pkg.Pipe(net, precision, device=device_index)
+    ctx = pipe.context(128)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+    x = torch.from_numpy(W.synthetic_positions(128, INPUT_SEED + 20)).to(dev).reshape(128, -1)
+    policy = torch.empty(128, 362, device=dev)
+    win = torch.empty(128, device=dev)
+    rows = []
+    for n in (1, 8, 32, 128):
+        for _ in range(5):
+            ctx.forward_heads_device(x.data_ptr(), n, 1.0, policy.data_ptr(), win.data_ptr())
+        ctx.sync()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        steps = 20
+        with torch.cuda.stream(stream):
+            a.record(stream)
+            for _ in range(steps):
+                ctx.forward_heads_device(x.data_ptr(), n, 1.0, policy.data_ptr(), win.data_ptr())
+            b.record(stream)
+        ctx.sync()
+        ms = a.elapsed_time(b) / steps
+        rows.append({"batch": n, "ms_per_step": ms, "positions_per_s": n / (ms * 1e-3)})
+    ctx.close()
+    pipe.close()
+    return {"workload": "config 2: 20 blocks x 256 filters, one GPU, device-resident, back-to-back steps",
+            "precision": precision, "rows": rows}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -237,8 +275,10 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-strict-mode", action="store_true",
-                    help="skip the extra timing of the fp16x2 mode")
+    ap.add_argument("--no-fast-mode", action="store_true",
+                    help="skip the extra timing of the plain fp16 mode")
+    ap.add_argument("--no-sweep", action="store_true",
+                    help="skip the batch sweep of the 20-block network (config 2)")
     ap.add_argument("--precision", default=PRECISION,
                     choices=["fp16", "bf16", "fp16-winograd", "bf16-winograd", "fp32", "fp16x2", "fp16x3"])
     args = ap.parse_args()
@@ -273,6 +313,10 @@ def main():
     x_np = W.synthetic_positions(ROT * B, INPUT_SEED + rank).reshape(ROT, B, -1)
     x_host = torch.from_numpy(x_np).pin_memory()
     x_dev = x_host.to(dev)
+    t0 = time.perf_counter()
+    packed_np = pkg.pack_positions(x_np.reshape(ROT * B, 18, 361)).reshape(ROT, B, -1)
+    pack_us_per_batch = (time.perf_counter() - t0) / ROT * 1e6
+    packed_host = torch.from_numpy(packed_np.view(np.int32)).pin_memory()
     policy_dev = torch.empty(B, 362, device=dev)
     win_dev = torch.empty(B, device=dev)
     policy_host = torch.empty(B, 362).pin_memory()
@@ -288,9 +332,40 @@ def main():
         ctx.forward_heads_device(x_dev[i % ROT].data_ptr(), B, 1.0, policy_dev.data_ptr(),
                                  win_dev.data_ptr())
 
-    def step_host(i):
-        ctx.forward_heads_ptr(x_host[i % ROT].data_ptr(), B, 1.0, policy_host.data_ptr(),
-                              win_host.data_ptr())
+    def timed_host(steps, warmup, lanes=2):
+        """End to end: every step copies its bit-packed positions from pinned host
+        memory, evaluates them and reads policy and winrate back, through the
+        blocking C-ABI call; `lanes` host threads with a context each keep the GPU
+        fed while a call's results travel.  Wall clock over all steps."""
+        import threading
+        ctxs = [pipe.context(B) for _ in range(lanes)]
+        outs = [(torch.empty(B, 362).pin_memory(), torch.empty(B).pin_memory()) for _ in range(lanes)]
+
+        def run(lane, first, count):
+            c, (pol, win) = ctxs[lane], outs[lane]
+            for i in range(first, first + count):
+                c.forward_heads_packed_ptr(packed_host[i % ROT].data_ptr(), B, 1.0, pol.data_ptr(),
+                                           win.data_ptr())
+
+        def phase(first, total):
+            per = [total // lanes + (1 if l < total % lanes else 0) for l in range(lanes)]
+            ts = [threading.Thread(target=run, args=(l, first + sum(per[:l]), per[l])) for l in range(lanes)]
+            [t.start() for t in ts]
+            [t.join() for t in ts]
+
+        phase(0, max(warmup, lanes))
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        phase(warmup, steps)
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3
+        barrier()
+        policy_host.copy_(outs[0][0])
+        win_host.copy_(outs[0][1])
+        for c in ctxs:
+            c.close()
+        return max_over_ranks(ms, world, dev) / steps
 
     def timed(step_fn, steps, warmup):
         for i in range(warmup):
@@ -317,7 +392,7 @@ def main():
 
     sampler = ClockSampler(local) if rank == 0 else None
     ms_dev, launches = timed(step_device, args.steps, args.warmup)
-    ms_e2e, _ = timed(step_host, args.steps, args.warmup)
+    ms_e2e = timed_host(args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
 
     # per-kernel durations of the same workload, measured with CUDA events on
@@ -358,7 +433,12 @@ def main():
                        "micro_batch": micro, "parallelism": "replicas, positions sharded, no collective",
                        "l2": "256 MB buffer written between timed steps (L2 flush); weights 378 MB > L2"},
             "e2e": {"value": e2e, "unit": "positions/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": B * 18 * 361 * 4, "d2h_bytes_per_step": B * 363 * 4},
+                    "h2d_bytes_per_step": B * 18 * 12 * 4, "d2h_bytes_per_step": B * 363 * 4,
+                    "note": "lzb_ctx_forward_heads_packed (blocking) on pinned host buffers: positions as bit "
+                            "planes (813 B each), policy and winrate read back; two host threads with a "
+                            "context each, wall clock over all steps; no L2 flush here, the 0.4 GB of "
+                            "weights each step streams exceed L2",
+                    "host_pack_us_per_batch": pack_us_per_batch},
             "gpu_launches": launches,
             "outputs_valid": pol_ok,
             "clocks": clocks,
@@ -368,6 +448,7 @@ def main():
                 "tflops": value * FLOPS_DIRECT / 1e12,
                 "frac_of_burst_peak": value * FLOPS_DIRECT / 1e12 / peaks["bf16_tflops"],
                 "frac_of_sustained_peak": value * FLOPS_DIRECT / 1e12 / peaks["bf16_tflops_sustained"],
+                "frac_of_nominal_fp16_dense_peak": value * FLOPS_DIRECT / 1e12 / world / 2250.0,
                 "per_gpu_tflops": value * FLOPS_DIRECT / 1e12 / world},
             "roofline": {"kernel": ("gemm_tc_kernel (36 Winograd channel contractions, tcgen05)" if winograd
                                     else ("conv_direct2_kernel" if B > 11 else "conv_ksplit_kernel") +
@@ -375,26 +456,31 @@ def main():
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "peak_source": peaks["source"] + " sustained bf16",
                          "flops_per_launch": flops_per_launch, "avg_launch_ms": avg_s * 1e3,
-                         "traffic": (GEMM_DRAM_BYTES_PER_LAUNCH if args.precision == "fp16" and B == BATCH else None)},
+                         "traffic": (GEMM_DRAM_BYTES_PER_LAUNCH.get(args.precision) if B == BATCH else None),
+                         "traffic_source": "ncu capture of this kernel on this workload (dram bytes read + "
+                                           "written, mean over the launches of one step), not measured in this run"},
             "kernel_time_share": {k: (v[0] / total_ms if total_ms else 0.0) for k, v in prof.items()},
             "kernel_ms_per_step": {k: v[0] / prof_steps for k, v in prof.items()},
         }
-        if world == 1 and args.precision == "fp16" and not args.no_strict_mode:
-            # The same workload in the mode that holds the half-precision accuracy
-            # bounds for every position of this 40-block network (activations as
-            # fp16 + e5m2): a second figure beside the headline, device-resident.
+        out["accuracy"] = ("policy <= 2e-3 and winrate <= 5e-3 max-abs against the reference CPUPipe on every "
+                           "position (tests/test_gpu_parity.py::test_config3_40x256_batch256)"
+                           if args.precision == PRECISION else "see tests/test_gpu_parity.py for this mode")
+        if world == 1 and args.precision == PRECISION and not args.no_fast_mode:
+            # The same workload in plain fp16, device-resident: faster, but its winrate
+            # error reaches 7e-3 on this network (bound 5e-3; 95 % of positions inside).
             ctx.close()
             pipe.close()
-            pipe = pkg.Pipe(net, "fp16x2", device=local)
+            pipe = pkg.Pipe(net, FAST_PRECISION, device=local)
             ctx = pipe.context(B)
             stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
-            ms_strict, _ = timed(step_device, args.steps, args.warmup)
-            out["strict_accuracy_mode"] = {
-                "precision": "fp16x2", "value": whole_job_rate(B, world, ms_strict), "unit": "positions/s",
-                "ms_per_step": ms_strict,
-                "note": "policy <= 2e-3 and winrate <= 5e-3 against the reference for every position "
-                        "(tests/test_gpu_parity.py::test_config3_40x256_batch256); the headline mode "
-                        "holds the winrate bound for 95 % of positions"}
+            ms_fast, _ = timed(step_device, args.steps, args.warmup)
+            out["fast_mode"] = {
+                "precision": FAST_PRECISION, "value": whole_job_rate(B, world, ms_fast), "unit": "positions/s",
+                "ms_per_step": ms_fast,
+                "note": "misses the winrate bound: max-abs 7.0e-3 over 256 positions (policy 1.6e-3); "
+                        "95th percentile 4.2e-3"}
+        if world == 1 and args.precision == PRECISION and not args.no_sweep:
+            out["config2_sweep"] = config2_sweep(pkg, W, torch, dev, local, args.precision)
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             sys.path.insert(0, os.path.join(ROOT, "oracle"))

@@ -54,7 +54,9 @@ extern "C" {
  *                      LZB_FP16 on deep networks.  Rounding errors made in the
  *                      first blocks are the ones the rest of the tower
  *                      amplifies, so by default only the first half of a tower
- *                      deeper than 24 blocks carries the low plane
+ *                      deeper than 24 blocks carries the low plane, and the
+ *                      first 4 blocks also correct the rounding of their
+ *                      weights with a third pair of e5m2 planes
  *                      (lzb_pipe_set_low_plane_blocks); holds the
  *                      half-precision bounds (policy 2e-3, winrate 5e-3) for
  *                      every position at 40 blocks.
@@ -100,15 +102,19 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks,
 void lzb_pipe_destroy(lzb_pipe* p);
 
 /*
- * LZB_FP16_X2 pipes only, before the first layer is pushed: carry the e5m2
- * low plane of the activations through the first `n` residual blocks (and the
- * input convolution) and run the blocks after them on the fp16 plane alone.
- * n < 0 or n > blocks: every block.  The default is every block for towers of
- * up to 24 blocks and the first half of deeper ones (see LZB_FP16_X2 above).
- * Precision selection has no finer grain in the reference
+ * LZB_FP16_X2 pipes only, before the first layer is pushed: which part of the
+ * tower carries the correction planes.  The first `activation_blocks` residual
+ * blocks (and the input convolution) carry the e5m2 low plane of the
+ * activations; the first `weight_blocks` of them (at most activation_blocks)
+ * also correct the rounding of their weights (a third e5m2 plane pair); the
+ * blocks after them run on the fp16 plane alone.  A negative or too large count
+ * means "as many as possible"; weight_blocks 0 switches the weight correction
+ * off altogether.  Defaults: every block for towers of up to 24 blocks and the
+ * first half of deeper ones; weights corrected in the first 4 blocks.
+ * Precision selection has no finer grain than half/single in the reference
  * (cfg_precision, src/Network.cpp:417-493); this knob has no counterpart there.
  */
-int lzb_pipe_set_low_plane_blocks(lzb_pipe* p, int n);
+int lzb_pipe_set_low_plane_blocks(lzb_pipe* p, int activation_blocks, int weight_blocks);
 
 /*
  * Upload one 3x3 convolution layer.  `layer` 0 is the input convolution

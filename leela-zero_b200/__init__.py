@@ -57,7 +57,7 @@ def lib():
         vp = ctypes.c_void_p
         L.lzb_pipe_create.argtypes = [ctypes.POINTER(vp)] + [ctypes.c_int] * 4
         L.lzb_pipe_destroy.argtypes = [vp]
-        L.lzb_pipe_set_low_plane_blocks.argtypes = [vp, ctypes.c_int]
+        L.lzb_pipe_set_low_plane_blocks.argtypes = [vp, ctypes.c_int, ctypes.c_int]
         L.lzb_pipe_push_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
         L.lzb_pipe_push_head_convs.argtypes = [vp, _f32p, _f32p]
         L.lzb_pipe_push_heads.argtypes = [vp] + [_f32p] * 10
@@ -122,20 +122,22 @@ class Pipe:
     ``[36][c_in][C]``), ``bn_mean``, ``bn_invstd`` (lists of ``[C]``),
     ``pol_w`` ``[2][C]``, ``val_w`` ``[1][C]``, plus optionally ``heads``.
     ``low_plane_blocks`` (``"fp16x2"`` only) overrides how many residual blocks carry
-    the e5m2 plane of the activations.  With ``from_filters`` the layers come from ``net["filters"]`` (untransformed
+    the e5m2 plane of the activations, ``weight_blocks`` how many of them also
+    correct their weights.  With ``from_filters`` the layers come from ``net["filters"]`` (untransformed
     ``[C][c_in][3][3]``, as ``weights.load_network`` returns them) instead of ``U``.
     """
 
     def __init__(self, net, precision="fp16", device=0, heads=True, from_filters=False,
-                 low_plane_blocks=None):
+                 low_plane_blocks=None, weight_blocks=None):
         L = lib()
         self.h = ctypes.c_void_p()
         self.channels, self.blocks = net["channels"], net["blocks"]
         self.precision = PRECISIONS[precision] if isinstance(precision, str) else precision
         check(L.lzb_pipe_create(ctypes.byref(self.h), device, self.channels, self.blocks,
                                 self.precision))
-        if low_plane_blocks is not None:     # fp16x2: blocks that carry the e5m2 plane (-1 = all)
-            check(L.lzb_pipe_set_low_plane_blocks(self.h, low_plane_blocks))
+        if low_plane_blocks is not None:     # fp16x2: blocks that carry the e5m2 planes (-1 = all)
+            check(L.lzb_pipe_set_low_plane_blocks(self.h, low_plane_blocks,
+                                                  4 if weight_blocks is None else weight_blocks))
         for l in range(len(net["bn_mean"])):
             mean = _ptr(np.ascontiguousarray(net["bn_mean"][l], np.float32))
             inv = _ptr(np.ascontiguousarray(net["bn_invstd"][l], np.float32))
@@ -224,6 +226,10 @@ class Context:
 
     def forward_heads_ptr(self, in_ptr, n, temp, policy_ptr, win_ptr):
         check(lib().lzb_ctx_forward_heads(self.h, in_ptr, n, temp, policy_ptr, win_ptr))
+
+    def forward_heads_packed_ptr(self, packed_ptr, n, temp, policy_ptr, win_ptr):
+        """Bit-packed positions and results at raw host pointers (pinned buffers); blocking."""
+        check(lib().lzb_ctx_forward_heads_packed(self.h, packed_ptr, n, temp, policy_ptr, win_ptr))
 
     def forward_device(self, in_dev, n, pol_dev, val_dev):
         """Device pointers, enqueued on the context's stream; no wait."""

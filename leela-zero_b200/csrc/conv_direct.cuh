@@ -202,6 +202,56 @@ __device__ __forceinline__ uint32_t e5m2_from_float(float v) {
 __device__ __forceinline__ float e5m2_to_float(uint32_t byte) {
     return __half2float(__ushort_as_half(static_cast<unsigned short>((byte & 0xFFu) << 8)));
 }
+// Two at a time with the hardware conversions (one rounding, saturating):
+// byte 0 of the result is `even`, byte 1 is `odd`.
+__device__ __forceinline__ uint32_t e5m2x2_from_floats(float even, float odd) {
+    unsigned short d;
+    asm("cvt.rn.satfinite.e5m2x2.f32 %0, %1, %2;" : "=h"(d) : "f"(odd), "f"(even));
+    return d;
+}
+__device__ __forceinline__ float2 e5m2x2_to_float2(uint32_t two_bytes) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(static_cast<unsigned short>(two_bytes)));
+    return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+// fp16 x2 -> e5m2 x2 and back, and fp32 arithmetic that takes an fp16 operand
+// as it is (sm_100 mixed-precision add / fma): the conversion unit runs at a
+// quarter of the arithmetic rate, and the two epilogue warps of a scheduler
+// share it, so the epilogue converts as little as it can.
+__device__ __forceinline__ uint32_t e5m2x2_from_half2(uint32_t h2) {
+    unsigned short d;
+    asm("cvt.rn.satfinite.e5m2x2.f16x2 %0, %1;" : "=h"(d) : "r"(h2));
+    return d;
+}
+__device__ __forceinline__ uint32_t half2_from_e5m2x2(uint32_t two_bytes) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(h2) : "h"(static_cast<unsigned short>(two_bytes)));
+    return h2;
+}
+// c + h, h the low (or high) half of a packed fp16 pair
+__device__ __forceinline__ float add_half_lo(uint32_t h2, float c) {
+    float d;
+    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(static_cast<unsigned short>(h2)), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float add_half_hi(uint32_t h2, float c) {
+    float d;
+    asm("add.rn.f32.f16 %0, %1, %2;" : "=f"(d) : "h"(static_cast<unsigned short>(h2 >> 16)), "f"(c));
+    return d;
+}
+// c - h
+__device__ __forceinline__ float minus_half_lo(uint32_t h2, float c) {
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(static_cast<unsigned short>(h2)),
+        "h"(static_cast<unsigned short>(0xBC00)), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float minus_half_hi(uint32_t h2, float c) {
+    float d;
+    asm("fma.rn.f32.f16 %0, %1, %2, %3;" : "=f"(d) : "h"(static_cast<unsigned short>(h2 >> 16)),
+        "h"(static_cast<unsigned short>(0xBC00)), "f"(c));
+    return d;
+}
 // 32 bytes (32 channels) of an e5m2 residual row, or zeros.
 __device__ __forceinline__ void load_residual8(uint4 (&v)[2], const unsigned char* src, bool use) {
 #pragma unroll
@@ -209,15 +259,22 @@ __device__ __forceinline__ void load_residual8(uint4 (&v)[2], const unsigned cha
         v[i] = use ? reinterpret_cast<const uint4*>(src)[i] : make_uint4(0u, 0u, 0u, 0u);
     }
 }
+// Scale between the fp16 plane and its e5m2 copy "hi8" (and, inversely, on the
+// e5m2 plane of the weight remainders it is multiplied with): w - fp16(w) is
+// around 2^-12 |w|, below the e5m2 range for typical filters, so the remainder
+// is stored times 256 and the activations divided by 256.
+constexpr float kHi8Scale = 1.0f / 256.0f;
+constexpr float kWLoScale = 256.0f;
 // epilogue_chunk for that form: the residual is fp16 + e5m2, the result is
 // split into an fp16 tile (written to the staging tile like epilogue_chunk
-// does) and 32 e5m2 bytes returned in lo[8] (byte c of the row = channel c).
+// does) and 32 e5m2 bytes returned in lo[8] (byte c of the row = channel c);
+// with want_h8, h8[8] receives the fp16 values scaled by kHi8Scale in e5m2.
 template <typename T>
 __device__ __forceinline__ void epilogue_chunk_e5m2(const uint32_t (&r)[32], const uint4 (&rv)[4],
                                                     const uint4 (&rl)[2], const float* s_scale,
                                                     const float* s_bias, bool use_res, bool interior,
                                                     unsigned char* stg_row, int lane,
-                                                    uint32_t (&lo)[8]) {
+                                                    uint32_t (&lo)[8], uint32_t (&h8)[8], bool want_h8) {
     const T tag = T();
     const float4* sc4 = reinterpret_cast<const float4*>(s_scale);
     const float4* bi4 = reinterpret_cast<const float4*>(s_bias);
@@ -231,27 +288,30 @@ __device__ __forceinline__ void epilogue_chunk_e5m2(const uint32_t (&r)[32], con
         const float bi[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         const uint32_t rr[4] = {rv[v].x, rv[v].y, rv[v].z, rv[v].w};
         uint32_t o[4];
-        uint32_t packed[2] = {0u, 0u};
+        uint32_t packed[2] = {0u, 0u}, packed8[2] = {0u, 0u};
 #pragma unroll
         for (int h = 0; h < 4; ++h) {
             float a = fmaf(__uint_as_float(r[8 * v + 2 * h]), sc[2 * h], bi[2 * h]);
             float b = fmaf(__uint_as_float(r[8 * v + 2 * h + 1]), sc[2 * h + 1], bi[2 * h + 1]);
             if (use_res) {
-                const float2 f = Vec2<T>::unpack(rr[h]);
                 // channels 8v + 2h, +1 are bytes (2h, 2h + 1) & 3 of word 2v + h / 2
-                const uint32_t w = lw[2 * v + (h >> 1)] >> (16 * (h & 1));
-                a += f.x + e5m2_to_float(w);
-                b += f.y + e5m2_to_float(w >> 8);
+                const uint32_t g = half2_from_e5m2x2(lw[2 * v + (h >> 1)] >> (16 * (h & 1)));
+                a = add_half_lo(g, add_half_lo(rr[h], a));
+                b = add_half_hi(g, add_half_hi(rr[h], b));
             }
             a = interior ? fmaxf(a, 0.f) : 0.f;
             b = interior ? fmaxf(b, 0.f) : 0.f;
             o[h] = pack2(tag, a, b);
-            const float2 hi = Vec2<T>::unpack(o[h]);
-            const uint32_t two = e5m2_from_float(a - hi.x) | (e5m2_from_float(b - hi.y) << 8);
-            packed[h >> 1] |= two << (16 * (h & 1));
+            packed[h >> 1] |= e5m2x2_from_floats(minus_half_lo(o[h], a), minus_half_hi(o[h], b)) << (16 * (h & 1));
+            if (want_h8) {
+                const __half2 scaled = __hmul2(*reinterpret_cast<const __half2*>(&o[h]), __float2half2_rn(kHi8Scale));
+                packed8[h >> 1] |= e5m2x2_from_half2(*reinterpret_cast<const uint32_t*>(&scaled)) << (16 * (h & 1));
+            }
         }
         lo[2 * v] = packed[0];
         lo[2 * v + 1] = packed[1];
+        h8[2 * v] = packed8[0];
+        h8[2 * v + 1] = packed8[1];
         *reinterpret_cast<uint4*>(stg_row + ((v ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }
@@ -574,17 +634,26 @@ __global__ void widen_weights_kernel(const float* __restrict__ Wd32, T* __restri
     }
 }
 
-// The weights once more in e5m2, for the MMAs of an e5m2 activation plane:
-// Wd32[9][Kp][Cin_p] fp32 -> W8[9][Kp][Cin8] bytes, Cin8 = Cin_p rounded up to
-// 128 (one 128-byte swizzle row), zero padded.
+// The weights once more in e5m2, for the MMAs of the e5m2 activation planes:
+// Wd32[9][Kp][Cin_p] fp32 -> W8[9][Kp][Cin8] bytes, zero padded (Cin8 a multiple
+// of 128, one 128-byte swizzle row).  Bytes [0, Cin_p): e5m2(w), the partner of
+// the activations' low plane.  With with_remainder, bytes [Cin_p, 2 Cin_p):
+// e5m2(kWLoScale (w - fp16(w))), the partner of the activations' hi8 plane.
 __global__ void weights_to_e5m2_kernel(const float* __restrict__ Wd32, unsigned char* __restrict__ W8,
-                                       int Cin_p, int Cin8, int Kp) {
+                                       int Cin_p, int Cin8, int Kp, int with_remainder) {
     const size_t total = (size_t)9 * Kp * Cin8;
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
          i += (size_t)gridDim.x * blockDim.x) {
         const int c = i % Cin8;
         const size_t row = i / Cin8;
-        W8[i] = c < Cin_p ? static_cast<unsigned char>(e5m2_from_float(Wd32[row * Cin_p + c])) : 0;
+        uint32_t b = 0;
+        if (c < Cin_p) {
+            b = e5m2_from_float(Wd32[row * Cin_p + c]);
+        } else if (with_remainder && c < 2 * Cin_p) {
+            const float w = Wd32[row * Cin_p + c - Cin_p];
+            b = e5m2_from_float(kWLoScale * (w - __half2float(__float2half_rn(w))));
+        }
+        W8[i] = static_cast<unsigned char>(b);
     }
 }
 

@@ -123,13 +123,16 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
 // is paired with activation chunk c - achunks (the weights may repeat the activations
 // against a second, "low" set of weight planes).  kPlanes : 1, or 2 when the
 // activations are carried as two 16-bit planes (high in channels [0, Kp), low in
-// [Kp, 2 Kp) of tmO and res, see epilogue_chunk_x2), or 3 when the low plane is
-// e5m2: a cell row is [Kp x 16 bits | Kp bytes]; chunks c >= achunks then come
-// from tmXl / tmWl (byte maps, 128 channels per 128-byte chunk) and are
-// multiplied by kind::f8f6f4 MMAs, and the low output plane (out_lo: its first
-// byte, out_pitch bytes per cell row, rows below q_rows exist) is written with
-// plain 32-byte stores, one sector per cell and chunk, straight from the
-// registers.  tmXl, tmWl, out_lo are ignored otherwise.
+// [Kp, 2 Kp) of tmO and res, see epilogue_chunk_x2), or 3 when low planes are
+// e5m2: a cell row is [Kp x 16 bits | Kp bytes lo | (Kp bytes hi8)]; chunks
+// c >= fchunks then come from tmXl / tmWl (byte maps, 128 channels per 128-byte
+// chunk) and are multiplied by kind::f8f6f4 MMAs.  The byte planes of the
+// output are written with plain 32-byte stores, one sector per cell and chunk,
+// straight from the registers: out_lo (x - fp16(x) in e5m2, the residual reads it
+// back) and, where the next layer corrects its weights as well, out_hi8
+// (fp16(x) / 256 in e5m2, the operand of that layer's e5m2(256 (w - fp16(w)))
+// plane); either may be null; out_pitch bytes per cell row, rows below q_rows
+// exist.  tmXl, tmWl, out_lo, out_hi8 are ignored for the other kPlanes.
 // ldr : elements of T per cell row of the residual tensor (its rows may be
 // wider than Kp when the tensor also holds a low plane).
 //
@@ -145,7 +148,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int npairs, int nsplit,
     int* err, int achunks, const __grid_constant__ CUtensorMap tmXl,
     const __grid_constant__ CUtensorMap tmWl, int ldr, unsigned char* out_lo, int out_pitch,
-    int q_rows) {
+    int q_rows, int fchunks, unsigned char* out_hi8) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -241,8 +244,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                     if (!ok) break;
                     const uint32_t wf = map_to_cta(wfull_bar(wb), 0);
                     mbar_expect_tx_cluster(wf, kWinBytes);
-                    const bool low8 = kPlanes == 3 && c >= achunks;     // e5m2 chunk: byte coordinates
-                    const int wcol = low8 ? (c - achunks) * 128 : c * kChunkK;
+                    const bool low8 = kPlanes == 3 && c >= fchunks;     // e5m2 chunk: byte coordinates
+                    const int wcol = low8 ? (c - fchunks) * 128 : c * kChunkK;
                     tma_load_2d_pair(win_base + wb * kWinBytes, low8 ? &tmXl : &tmX,
                                      low8 ? wcol : (c < achunks ? c : c - achunks) * kChunkK,
                                      m0 - kWinPad, wf);
@@ -277,52 +280,106 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             uint32_t phase = 0, wphase = 0;
             bool ok = true;
             int local = 0;
-            for (int unit = unit_begin; unit < unit_end && ok; ++unit, ++local) {
-                const int acc = local & 1;
-                const uint32_t accphase = (local >> 1) & 1u;
-                ok = mbar_wait(tempty_bar(acc), accphase ^ 1u, abort_flag, err, kErrD2MmaAcc);
-                if (!ok) break;
-                tcgen05_fence_after();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kMaxN);
-                for (int c = 0; c < kchunks && ok; ++c) {
-                    ok = mbar_wait(wfull_bar(wb), wphase, abort_flag, err, kErrD2MmaFull);
+            if constexpr (!kSliced) {
+                // Whole tiles, one tap per stage.  This lane's instruction stream is what
+                // paces the tensor pipe (a 256 x 256 x 16 MMA lasts ~128 cycles, so a stage
+                // leaves ~500 cycles for everything between two waits): descriptors are a
+                // constant plus an address in 16-byte units, the nine row offsets of the
+                // window are immediates, and the two operand formats have a loop each.
+                const uint64_t dbase = umma_desc_sw128(0);
+                const uint32_t win16 = (win_base & 0x3FFFFu) >> 4, b16 = (b_base & 0x3FFFFu) >> 4;
+                for (int unit = unit_begin; unit < unit_end && ok; ++unit, ++local) {
+                    const int acc = local & 1;
+                    const uint32_t accphase = (local >> 1) & 1u;
+                    ok = mbar_wait(tempty_bar(acc), accphase ^ 1u, abort_flag, err, kErrD2MmaAcc);
                     if (!ok) break;
-                    const uint32_t win = win_base + wb * kWinBytes;
-                    const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
-                    for (int tap0 = 0; tap0 < 9; tap0 += taps_per_stage) {
-                        const int g = 9 - tap0 < taps_per_stage ? 9 - tap0 : taps_per_stage;
-                        ok = mbar_wait(bfull_bar(stage), phase, abort_flag, err, kErrD2MmaFull);
+                    tcgen05_fence_after();
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kMaxN);
+                    uint32_t accum = 0u;
+                    for (int c = 0; c < kchunks && ok; ++c) {
+                        ok = mbar_wait(wfull_bar(wb), wphase, abort_flag, err, kErrD2MmaFull);
                         if (!ok) break;
-                        tcgen05_fence_after();
-                        for (int j = 0; j < g; ++j) {
-                            const int tap = tap0 + j;
-                            const int row0 = kWinPad + (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
+                        const uint64_t a_win = dbase + (win16 + static_cast<uint32_t>(wb) * (kWinBytes >> 4));
+                        const bool f8 = kPlanes == 3 && c >= fchunks;
+#pragma unroll
+                        for (int tap = 0; tap < 9; ++tap) {
+                            ok = mbar_wait(bfull_bar(stage), phase, abort_flag, err, kErrD2MmaFull);
+                            if (!ok) break;
+                            // rows (24 + 20 dy + dx) .. of the window, 8 sixteen-byte units each
                             const uint64_t a_desc =
-                                umma_desc_sw128(win + static_cast<uint32_t>(row0) * 128u);
-                            const uint64_t b_desc =
-                                umma_desc_sw128(b_base + stage * kB2StageBytes + j * btx);
-                            if (kPlanes == 3 && c >= achunks) {
+                                a_win + static_cast<uint32_t>((kWinPad + (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1)) * 8);
+                            const uint64_t b_desc = dbase + (b16 + static_cast<uint32_t>(stage) * (kB2StageBytes >> 4));
+                            if (f8) {
 #pragma unroll
                                 for (int k = 0; k < 4; ++k) {
                                     tcgen05_mma_f8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc8, 1u);
                                 }
                             } else {
+                                tcgen05_mma_f16_pair(d_tmem, a_desc, b_desc, idesc, accum);
+                                accum = 1u;
 #pragma unroll
-                                for (int k = 0; k < kChunkK / 16; ++k) {
-                                    tcgen05_mma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
-                                                         (c > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                                for (int k = 1; k < kChunkK / 16; ++k) {
+                                    tcgen05_mma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, 1u);
                                 }
                             }
+                            tcgen05_commit_pair(bempty_bar(stage));
+                            if (++stage == nstages) { stage = 0; phase ^= 1u; }
                         }
-                        tcgen05_commit_pair(bempty_bar(stage));
-                        if (++stage == nstages) { stage = 0; phase ^= 1u; }
+                        if (!ok) break;
+                        tcgen05_commit_pair(wempty_bar(wb));
+                        if (++wb == nwin) { wb = 0; wphase ^= 1u; }
                     }
                     if (!ok) break;
-                    tcgen05_commit_pair(wempty_bar(wb));
-                    if (++wb == nwin) { wb = 0; wphase ^= 1u; }
+                    tcgen05_commit_pair(tfull_bar(acc));
                 }
-                if (!ok) break;
-                tcgen05_commit_pair(tfull_bar(acc));
+            } else {
+                for (int unit = unit_begin; unit < unit_end && ok; ++unit, ++local) {
+                    const int acc = local & 1;
+                    const uint32_t accphase = (local >> 1) & 1u;
+                    ok = mbar_wait(tempty_bar(acc), accphase ^ 1u, abort_flag, err, kErrD2MmaAcc);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kMaxN);
+                    for (int c = 0; c < kchunks && ok; ++c) {
+                        ok = mbar_wait(wfull_bar(wb), wphase, abort_flag, err, kErrD2MmaFull);
+                        if (!ok) break;
+                        const uint32_t win = win_base + wb * kWinBytes;
+                        const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
+                        for (int tap0 = 0; tap0 < 9; tap0 += taps_per_stage) {
+                            const int g = 9 - tap0 < taps_per_stage ? 9 - tap0 : taps_per_stage;
+                            ok = mbar_wait(bfull_bar(stage), phase, abort_flag, err, kErrD2MmaFull);
+                            if (!ok) break;
+                            tcgen05_fence_after();
+                            for (int j = 0; j < g; ++j) {
+                                const int tap = tap0 + j;
+                                const int row0 = kWinPad + (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
+                                const uint64_t a_desc =
+                                    umma_desc_sw128(win + static_cast<uint32_t>(row0) * 128u);
+                                const uint64_t b_desc =
+                                    umma_desc_sw128(b_base + stage * kB2StageBytes + j * btx);
+                                if (kPlanes == 3 && c >= fchunks) {
+#pragma unroll
+                                    for (int k = 0; k < 4; ++k) {
+                                        tcgen05_mma_f8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc8, 1u);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int k = 0; k < kChunkK / 16; ++k) {
+                                        tcgen05_mma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc,
+                                                             (c > 0 || tap > 0 || k > 0) ? 1u : 0u);
+                                    }
+                                }
+                            }
+                            tcgen05_commit_pair(bempty_bar(stage));
+                            if (++stage == nstages) { stage = 0; phase ^= 1u; }
+                        }
+                        if (!ok) break;
+                        tcgen05_commit_pair(wempty_bar(wb));
+                        if (++wb == nwin) { wb = 0; wphase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    tcgen05_commit_pair(tfull_bar(acc));
+                }
             }
         }
     } else {
@@ -365,14 +422,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
                             const uint4 (&e)[2], int col) {
                 wait_staged_tile_read(lane);
                 if constexpr (e5) {
-                    uint32_t lo[8];
+                    uint32_t lo[8], h8[8];
                     epilogue_chunk_e5m2<T>(r, v, e, s_scale + col, s_bias + col, use_res, interior, stg_row,
-                                           lane, lo);
+                                           lane, lo, h8, out_hi8 != nullptr);
                     store_staged_tile(&tmO, stg, col, row0, lane);
                     if (q < q_rows) {
-                        uint4* dst = reinterpret_cast<uint4*>(out_lo + static_cast<size_t>(q) * out_pitch + col);
-                        dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                        dst[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                        const size_t off = static_cast<size_t>(q) * out_pitch + col;
+                        if (out_lo != nullptr) {
+                            uint4* dst = reinterpret_cast<uint4*>(out_lo + off);
+                            dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                            dst[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                        }
+                        if (out_hi8 != nullptr) {
+                            uint4* dst = reinterpret_cast<uint4*>(out_hi8 + off);
+                            dst[0] = make_uint4(h8[0], h8[1], h8[2], h8[3]);
+                            dst[1] = make_uint4(h8[4], h8[5], h8[6], h8[7]);
+                        }
                     }
                 } else if constexpr (!two) {
                     epilogue_chunk<T>(r, v, s_scale + col, s_bias + col, use_res, interior, stg_row, lane);

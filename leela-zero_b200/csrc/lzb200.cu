@@ -21,6 +21,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #include "conv_direct.cuh"
@@ -127,6 +128,7 @@ struct Layer {
     unsigned char* Wd8 = nullptr;   // e5m2 copy of the weights [9][Kp][cin8] (LZB_FP16_X2), or null
     int lchunks = 0;            // 128-channel e5m2 chunks that follow the fp16 chunks
     bool out_lo = false;        // this layer writes an e5m2 low plane beside its fp16 output
+    bool out_hi8 = false;       // ... and an e5m2 copy of the fp16 plane (the next layer corrects its weights)
     CUtensorMap tmW8[5];        // byte maps over Wd8, box 128 x Kp/(2*ns)
     CUtensorMap tmW;            // box 64 x Kp   (one CTA per tile)
     CUtensorMap tmW2[5];        // CTA pairs: [ns] has box 64 x Kp/(2*ns), ns = 1..4 where valid
@@ -153,11 +155,16 @@ struct lzb_pipe {
     int aplanes = 1;            // activations carried as hi + lo: 2 = two 16-bit planes (LZB_FP16_X3),
                                 // 3 = a 16-bit plane and an e5m2 plane (LZB_FP16_X2)
     // bytes of one cell row of the activation tensors
-    int row_bytes() const { return aplanes == 3 ? 3 * Cp : aplanes * Cp * elt; }
+    int row_bytes() const { return aplanes == 3 ? (wlo_layers > 1 ? 4 : 3) * Cp : aplanes * Cp * elt; }
     // LZB_FP16_X2: layers 0 .. lo_layers-1 write the e5m2 plane and layers
     // 1 .. lo_layers-1 read it; the layers after them run on the fp16 plane alone
     // (same buffers, the low bytes of a row are then neither written nor read).
     int lo_layers = 0;
+    // Layers 0 .. wlo_layers-1 (a prefix of those) also correct the rounding of
+    // their weights: they read a third plane, e5m2(fp16(x) / 256), against
+    // e5m2(256 (w - fp16(w))); a cell row is then [Cp x fp16 | Cp lo | Cp hi8].
+    // The input convolution does the same with a second fp16 weight plane.
+    int wlo_layers = 0;
     bool wsplit = false;        // weights carried as hi + lo planes as well (LZB_FP16_X3)
     int elt = 2;        // bytes per stored element
     int sm_count = 0;
@@ -448,10 +455,12 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
         {
             LaunchScope scope(c, kClassContraction);
             auto kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 1, true> : dc2::conv_direct2_kernel<T, 1, false>;
-            if (p->aplanes == 2) {
-                kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 2, true> : dc2::conv_direct2_kernel<T, 2, false>;
-            } else if (L.out_lo || L.lchunks > 0) {
-                kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 3, true> : dc2::conv_direct2_kernel<T, 3, false>;
+            if constexpr (std::is_same<T, __half>::value) {     // the plane-splitting modes are fp16 only
+                if (p->aplanes == 2) {
+                    kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 2, true> : dc2::conv_direct2_kernel<T, 2, false>;
+                } else if (L.out_lo || L.lchunks > 0) {
+                    kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 3, true> : dc2::conv_direct2_kernel<T, 3, false>;
+                }
             }
             // the byte maps only matter to the e5m2 variant; any valid map serves the others
             const CUtensorMap& in_lo = tm_in_lo ? *tm_in_lo : tm_in;
@@ -459,10 +468,12 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
             const int ldr = p->row_bytes() / p->elt;
             unsigned char* out_lo =
                 (L.out_lo && out) ? static_cast<unsigned char*>(out) + (size_t)p->Cp * p->elt : nullptr;
+            unsigned char* out_hi8 =
+                (L.out_hi8 && out) ? static_cast<unsigned char*>(out) + (size_t)p->Cp * (p->elt + 1) : nullptr;
             le = cudaLaunchKernelEx(&cfg, kernel, tm_in, L.tmW2[nsplit], tm_out, res,
                                     (const float*)L.mean, (const float*)L.invstd, Q, p->Cp,
                                     kchunks + L.lchunks, npairs, nsplit, c->d_err, L.achunks, in_lo, w_lo,
-                                    ldr, out_lo, p->row_bytes(), c->Qa);
+                                    ldr, out_lo, p->row_bytes(), c->Qa, kchunks, out_hi8);
         }
         LZB_CUDA(le);
         LZB_CUDA(cudaGetLastError());
@@ -572,12 +583,8 @@ int set_smem_attrs() {
             (const void*)dc2::conv_direct2_kernel<__half, 1, false>, (const void*)dc2::conv_direct2_kernel<__half, 1, true>,
             (const void*)dc2::conv_direct2_kernel<__half, 2, false>, (const void*)dc2::conv_direct2_kernel<__half, 2, true>,
             (const void*)dc2::conv_direct2_kernel<__half, 3, false>, (const void*)dc2::conv_direct2_kernel<__half, 3, true>,
-            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 3, false>,
-            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 3, true>,
             (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, false>,
-            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, true>,
-            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 2, false>,
-            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 2, true>};
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, true>};
         for (const void* k : variants) {
             LZB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
         }
@@ -757,16 +764,24 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
     // The network input (layer 0) is exact in 16 bits and has no low plane.
     int wplanes = 1;
     unsigned lo_mask = 0;
+    bool remainder8 = false;         // this layer's e5m2 weights carry the remainder plane too
     if (p->direct) {
         const int act_planes = (p->aplanes == 2 && layer > 0) ? 2 : 1;
-        wplanes = act_planes + (p->wsplit ? 1 : 0);
-        if (p->wsplit) lo_mask = 1u << (wplanes - 1);
+        // the network input is exact in 16 bits: a layer-0 weight remainder is a second fp16 plane
+        const bool wsplit = p->wsplit || (p->aplanes == 3 && layer == 0 && p->wlo_layers > 0);
+        wplanes = act_planes + (wsplit ? 1 : 0);
+        if (wsplit) lo_mask = 1u << (wplanes - 1);
         L.cinw = L.cin_p * wplanes;
         L.achunks = L.cin_p * act_planes / 64;
-        // e5m2 low plane of the activations: 128 channels per chunk, none for the network
-        // input and none beyond the layers that carry the plane
-        L.lchunks = (p->aplanes == 3 && layer > 0 && layer < p->lo_layers) ? (L.cin_p + 127) / 128 : 0;
+        // e5m2 planes of the activations: 128 channels per chunk, none for the network
+        // input and none beyond the layers that carry them; lo alone, or lo and hi8
+        // (2 cin_p bytes, always whole chunks)
+        remainder8 = p->aplanes == 3 && layer > 0 && layer < p->wlo_layers;
+        if (p->aplanes == 3 && layer > 0 && layer < p->lo_layers) {
+            L.lchunks = remainder8 ? L.cin_p / 64 : (L.cin_p + 127) / 128;
+        }
         L.out_lo = p->aplanes == 3 && layer < p->lo_layers;
+        L.out_hi8 = p->aplanes == 3 && layer + 1 < p->wlo_layers;
     }
     float* Wd32 = nullptr;           // fp32 filters in the implicit-GEMM layout (widened modes)
     if (rc == LZB_OK && p->direct && src_is_filters) {
@@ -836,7 +851,7 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
             const int cin8 = L.lchunks * 128;
             e = cudaMalloc(&L.Wd8, (size_t)9 * p->Cp * cin8);
             if (e == cudaSuccess) {
-                dc::weights_to_e5m2_kernel<<<512, 256>>>(Wd32, L.Wd8, L.cin_p, cin8, p->Cp);
+                dc::weights_to_e5m2_kernel<<<512, 256>>>(Wd32, L.Wd8, L.cin_p, cin8, p->Cp, remainder8 ? 1 : 0);
                 e = cudaGetLastError();
             }
         }
@@ -881,18 +896,18 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
 
 namespace {
 // LZB_FP16_X2: how many residual blocks, counted from the input, carry the e5m2
-// low plane by default.  A rounding error made in block b is amplified by the
-// blocks after it, and most by the early ones, where the residual stream is
-// still small next to what a block adds to it: in a 40-block network the low
-// plane stops changing the final error somewhere between block 16 and 20, so
-// the first half of a deep tower carries it and shallow towers carry it
-// throughout.
-int default_low_plane_blocks(int blocks) {
-    if (const char* e = getenv("LZB_X2_BLOCKS")) {
-        const int n = atoi(e);
-        return (n < 0 || n > blocks) ? blocks : n;
-    }
-    return blocks <= 24 ? blocks : (blocks + 1) / 2;
+// low plane of the activations and how many also correct the rounding of
+// their weights.  A rounding error made in block b is amplified by the blocks
+// after it, and most by the early ones, where the residual stream is still
+// small next to what a block adds to it.  Measured on a 40-block network
+// (exact-accumulation emulation, 128 positions, winrate max-abs): fp16 weights
+// everywhere cost 5.1e-3, exact weights in the first 4 blocks alone bring that
+// to 1.6e-3; the activations' low plane stops paying somewhere after block 16.
+// So the first half of a deep tower carries the low plane (shallow towers
+// throughout) and the first 4 blocks correct their weights.
+void default_x2_blocks(int blocks, int* activation_blocks, int* weight_blocks) {
+    *activation_blocks = blocks <= 24 ? blocks : (blocks + 1) / 2;
+    *weight_blocks = blocks < 4 ? blocks : 4;
 }
 }  // namespace
 
@@ -963,7 +978,12 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     p->direct = direct;
     p->aplanes = aplanes;
     p->wsplit = wsplit;
-    if (aplanes == 3) p->lo_layers = 1 + 2 * default_low_plane_blocks(blocks);
+    if (aplanes == 3) {
+        int b0, b1;
+        default_x2_blocks(blocks, &b0, &b1);
+        p->lo_layers = 1 + 2 * b0;
+        p->wlo_layers = b1 > 0 ? 1 + 2 * b1 : 0;
+    }
     // CTA pairs are the default; LZB_CONV_PAIRS=0 selects the one-CTA-per-tile
     // kernel (kept as a cross-check and for diagnostics).
     p->pairs = direct && (aplanes >= 2 ||
@@ -983,14 +1003,18 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     return LZB_OK;
 }
 
-int lzb_pipe_set_low_plane_blocks(lzb_pipe* p, int n) {
+int lzb_pipe_set_low_plane_blocks(lzb_pipe* p, int activation_blocks, int weight_blocks) {
     if (!p) return fail(LZB_ERR_ARG, "null pipe");
-    if (p->aplanes != 3) return fail(LZB_ERR_ARG, "only LZB_FP16_X2 pipes carry a low plane");
+    if (p->aplanes != 3) return fail(LZB_ERR_ARG, "only LZB_FP16_X2 pipes carry low planes");
     for (const Layer& L : p->layers) {
         if (L.present) return fail(LZB_ERR_ARG, "set the low-plane blocks before the first layer is pushed");
     }
-    if (n < 0 || n > p->blocks) n = p->blocks;
-    p->lo_layers = 1 + 2 * n;
+    int b0 = activation_blocks, b1 = weight_blocks;
+    if (b0 < 0 || b0 > p->blocks) b0 = p->blocks;
+    if (b1 < 0 || b1 > b0) b1 = b0;
+    p->lo_layers = 1 + 2 * b0;
+    // no weight correction at all: not even the input convolution's
+    p->wlo_layers = weight_blocks == 0 ? 0 : 1 + 2 * b1;
     return LZB_OK;
 }
 
@@ -1154,8 +1178,10 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
             // the e5m2 planes: Cp bytes per row, after the 16-bit channels
             unsigned char* xl = static_cast<unsigned char*>(c->X) + 2 * p->Cp;
             unsigned char* hl = static_cast<unsigned char*>(c->H) + 2 * p->Cp;
-            if (!rc) rc = make_map_2d(&c->tmXl, -1, xl, (uint64_t)c->Qa, p->Cp, dc::kWinRows, 128, sw128, pitch);
-            if (!rc) rc = make_map_2d(&c->tmHl, -1, hl, (uint64_t)c->Qa, p->Cp, dc::kWinRows, 128, sw128, pitch);
+            // ... and, where weights are corrected too, the Cp bytes of the hi8 plane behind them
+            const uint64_t lb = (uint64_t)p->Cp * (p->wlo_layers > 1 ? 2 : 1);
+            if (!rc) rc = make_map_2d(&c->tmXl, -1, xl, (uint64_t)c->Qa, lb, dc::kWinRows, 128, sw128, pitch);
+            if (!rc) rc = make_map_2d(&c->tmHl, -1, hl, (uint64_t)c->Qa, lb, dc::kWinRows, 128, sw128, pitch);
         }
         if (rc) {
             lzb_ctx_destroy(c);
