@@ -292,7 +292,12 @@ int lzb_ctx_debug_wait_probe(lzb_ctx* c, int limit_ms);
  * `stream` (a cudaStream_t, NULL for the default stream) and not waited for.
  *
  * The first call on each device looks up the array's device address and sets
- * kernel attributes; make that first call outside any stream capture.  All
+ * kernel attributes; make that first call outside any stream capture.  It is
+ * also the moment at which the CUDA driver loads this library's code onto that
+ * device and with it sets the array aside (CUDA loads modules lazily, at first
+ * use), which takes device memory once: a host that hands all device memory to
+ * its own pool must make this first call BEFORE the pool takes the memory;
+ * later calls take nothing.  All
  * calls share the one array: it is rewritten (and cleared where needed) at the
  * start of each call, and two calls whose kernels overlap on the GPU, from
  * different streams or threads, race on it.  Serialise them.

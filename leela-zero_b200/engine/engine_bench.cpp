@@ -18,7 +18,24 @@
 //
 //   engine_bench --weights FILE [--threads T] [--batch B] [--gpus G] [--visits V]
 //                [--moves M] [--games N] [--batching eager|wait]
-//                [--precision fp16|fp16x2|bf16|fp32] [--verbose]
+//                [--precision auto|single|half|fp32|fp16|fp16x2|bf16|...]
+//                [--cpu-only] [--selfchecks K] [--deterministic BYTES]
+//                [--inject-half-init-failure N] [--verbose]
+//
+// --precision auto/single/half are the engine's own settings (cfg_precision,
+// src/GTP.h:103-107); a mode name selects half (or single for fp32) and the
+// arithmetic behind it.  --cpu-only is the engine's --cpu-only (cfg_cpu_only,
+// src/Network.cpp:579-581): the reference's CPUPipe instead of the GPU.
+// --selfchecks K forces the engine's built-in comparison of the GPU pipe with
+// its CPU pipe (src/Network.cpp:781-791) after each of the first K moves; a
+// mismatch ends the program like it ends the engine.
+// --deterministic BYTES makes a game repeatable so that two pipes can be
+// compared move by move: one search thread with a fixed random seed, no visit
+// limit, each search stopped by the tree-size limit BYTES
+// (cfg_max_tree_size, src/UCTSearch.cpp:645), which the search thread itself
+// checks after every simulation (the visit limit is polled by the main thread
+// every 10 ms, src/UCTSearch.cpp:797-823, so it stops at a different count on
+// every run).
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -39,15 +56,7 @@
 #include "UCTSearch.h"
 #include "Utils.h"
 #include "Zobrist.h"
-
-namespace lzb_engine {
-extern std::vector<int> gpus;
-extern CUDAPipe::Precision precision;
-extern std::atomic<unsigned long long> evals;
-extern CUDAPipe* last_pipe;
-extern int callers;
-extern bool eager;
-}  // namespace lzb_engine
+#include "cuda_scheduler.h"
 
 namespace {
 // N games at once on one shared network; returns the number of moves played.
@@ -80,12 +89,14 @@ int play_games(Network& network, int games, int moves) {
 }  // namespace
 
 int main(int argc, char** argv) {
-    std::string weights;
-    int threads = 8, batch = 8, ngpus = 1, visits = 1600, moves = 50, games = 1;
-    bool verbose = false;
+    std::string weights, precision = "auto", move_list;
+    int threads = 8, batch = 8, ngpus = 1, visits = 1600, moves = 50, games = 1, selfchecks = 0;
+    long long deterministic_bytes = 0;
+    bool verbose = false, cpu_only = false;
     for (int i = 1; i < argc; i++) {
         const std::string k = argv[i];
         if (k == "--verbose") { verbose = true; continue; }
+        if (k == "--cpu-only") { cpu_only = true; continue; }
         if (i + 1 >= argc) { std::fprintf(stderr, "missing value for %s\n", k.c_str()); return 2; }
         const std::string v = argv[++i];
         if (k == "--weights") weights = v;
@@ -95,18 +106,30 @@ int main(int argc, char** argv) {
         else if (k == "--visits") visits = std::atoi(v.c_str());
         else if (k == "--moves") moves = std::atoi(v.c_str());
         else if (k == "--games") games = std::atoi(v.c_str());
+        else if (k == "--selfchecks") selfchecks = std::atoi(v.c_str());
+        else if (k == "--deterministic") deterministic_bytes = std::atoll(v.c_str());
+        else if (k == "--inject-half-init-failure") lzb_engine::fail_half_init = std::atoi(v.c_str());
         else if (k == "--batching") lzb_engine::eager = (v == "eager");
-        else if (k == "--precision") {
-            lzb_engine::precision = v == "fp32" ? CUDAPipe::Precision::FP32
-                                  : v == "bf16" ? CUDAPipe::Precision::BF16
-                                  : v == "fp16x2" ? CUDAPipe::Precision::FP16_X2 : CUDAPipe::Precision::FP16;
-        } else { std::fprintf(stderr, "unknown option %s\n", k.c_str()); return 2; }
+        else if (k == "--precision") precision = v;
+        else { std::fprintf(stderr, "unknown option %s\n", k.c_str()); return 2; }
     }
     if (weights.empty()) { std::fprintf(stderr, "--weights is required\n"); return 2; }
-    lzb_engine::gpus.clear();
-    for (int g = 0; g < ngpus; g++) lzb_engine::gpus.push_back(g);
+    if (games < 1 || threads < 1) { std::fprintf(stderr, "bad --games/--threads\n"); return 2; }
 
     GTP::setup_default_parameters();
+    if (precision == "auto") cfg_precision = precision_t::AUTO;
+    else if (precision == "single") cfg_precision = precision_t::SINGLE;
+    else if (precision == "half") cfg_precision = precision_t::HALF;
+    else {
+        bool ok = false;
+        const auto mode = lzb_engine::precision_from_name(precision.c_str(), &ok);
+        if (!ok) { std::fprintf(stderr, "unknown precision %s\n", precision.c_str()); return 2; }
+        if (mode == CUDAPipe::Precision::FP32) cfg_precision = precision_t::SINGLE;
+        else { cfg_precision = precision_t::HALF; lzb_engine::half_mode = mode; }
+    }
+    cfg_cpu_only = cpu_only;
+    cfg_gpus.clear();
+    for (int g = 0; g < ngpus; g++) cfg_gpus.push_back(g);
     cfg_gtp_mode = true;
     cfg_num_threads = threads;
     cfg_batch_size = batch;
@@ -119,7 +142,13 @@ int main(int argc, char** argv) {
     cfg_resignpct = 0;
     cfg_quiet = !verbose;
     cfg_weightsfile = weights;
-    if (games < 1 || threads < 1) { std::fprintf(stderr, "bad --games/--threads\n"); return 2; }
+    if (deterministic_bytes > 0) {
+        if (games != 1) { std::fprintf(stderr, "--deterministic plays one game\n"); return 2; }
+        threads = 1;
+        cfg_num_threads = 1;
+        cfg_max_visits = UCTSearch::UNLIMITED_PLAYOUTS;
+        cfg_max_playouts = UCTSearch::UNLIMITED_PLAYOUTS;
+    }
     if (games > 1) {
         cfg_noise = true;          // autogtp's self-play options: -n, -m 30
         cfg_random_cnt = 30;
@@ -132,39 +161,73 @@ int main(int argc, char** argv) {
     Zobrist::init_zobrist(*rng);
     Random::get_Rng().seedrandom(cfg_rng_seed);
     Utils::create_z_table();
+    if (deterministic_bytes > 0) {
+        // The pool's one thread draws the random symmetries of the search
+        // (src/Network.cpp:776); its generator is otherwise seeded from the
+        // thread id (src/Random.cpp:46-51), which differs from run to run.
+        Utils::ThreadGroup tg(thread_pool);
+        tg.add_task([] { Random::get_Rng().seedrandom(12345); });
+        tg.wait_all();
+    }
     auto network = std::make_unique<Network>();
-    {
+    Network* net = network.get();
+    try {
         // the cache is sized from the playout limit (src/Network.cpp:578-587); N games share it
         const auto playouts = std::min(cfg_max_playouts, cfg_max_visits) * games;
         network->initialize(playouts, cfg_weightsfile);
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "network initialisation failed: %s\n", e.what());
+        return 3;
     }
+    const CUDAPipe* pipe = lzb_engine::last_pipe;
+    static const char* const mode_names[] = {"fp32", "fp16", "bf16", "fp16-winograd", "bf16-winograd",
+                                             "fp16x2", "fp16x3"};
+    const std::string pipe_name = cpu_only || !pipe ? "CPUPipe"
+        : std::string("CUDAPipe ") + mode_names[static_cast<int>(pipe->precision())];
     auto game = std::make_unique<GameState>();
     if (games == 1) {
         GTP::initialize(std::move(network));
         game->init_game(BOARD_SIZE, KOMI);
         game->set_timecontrol(0, 1, 0, 0);   // infinite time, as --benchmark does
     }
+    // after GTP::initialize, which sets the memory limits (src/GTP.cpp:395-412)
+    if (deterministic_bytes > 0) cfg_max_tree_size = static_cast<size_t>(deterministic_bytes);
 
     const auto evals0 = lzb_engine::evals.load();
     const auto t0 = std::chrono::steady_clock::now();
-    int played = 0;
-    if (games > 1) {
-        played = play_games(*network, games, moves);
-    } else {
-        for (int m = 0; m < moves; m++) {
-            GTP::execute(*game, (m % 2 == 0) ? "genmove b" : "genmove w");
-            played++;
-            if (game->get_passes() >= 2) break;
+    int played = 0, checked = 0;
+    try {
+        if (games > 1) {
+            played = play_games(*network, games, moves);
+        } else {
+            for (int m = 0; m < moves; m++) {
+                GTP::execute(*game, (m % 2 == 0) ? "genmove b" : "genmove w");
+                played++;
+                move_list += (m ? " " : "") + game->move_to_text(game->get_last_move());
+                if (checked < selfchecks) {
+                    // throws "OpenCL self-check mismatch." when the pipes differ by more than 0.2
+                    net->get_output(game.get(), Network::Ensemble::RANDOM_SYMMETRY, -1, false, false,
+                                    true);
+                    checked++;
+                }
+                if (game->get_passes() >= 2) break;
+            }
         }
+    } catch (const std::exception& e) {
+        std::fprintf(stderr, "engine failed: %s\n", e.what());
+        return 4;
     }
     const double sec = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     const auto evals = lzb_engine::evals.load() - evals0;
-    const auto s = lzb_engine::last_pipe ? lzb_engine::last_pipe->stats() : CUDAPipe::Stats();
-    std::printf("\n{\"games\": %d, \"moves\": %d, \"seconds\": %.3f, \"visits_per_move\": %d, \"threads\": %d, "
-                "\"batch\": %d, \"batching\": \"%s\", \"gpus\": %d, \"nn_evals\": %llu, \"nn_evals_per_s\": %.1f, "
-                "\"visits_per_s\": %.1f, \"batches\": %zu, \"mean_batch\": %.2f, \"timeouts\": %zu}\n",
-                games, played, sec, visits, threads, batch, lzb_engine::eager ? "eager" : "wait", ngpus, evals, evals / sec,
+    const auto s = pipe && !cpu_only ? pipe->stats() : CUDAPipe::Stats();
+    std::printf("\n{\"pipe\": \"%s\", \"games\": %d, \"moves\": %d, \"seconds\": %.3f, \"visits_per_move\": %d, "
+                "\"threads\": %d, \"batch\": %d, \"batching\": \"%s\", \"gpus\": %d, \"nn_evals\": %llu, "
+                "\"nn_evals_per_s\": %.1f, \"visits_per_s\": %.1f, \"batches\": %zu, \"mean_batch\": %.2f, "
+                "\"timeouts\": %zu, \"halted\": %zu, \"selfchecks_passed\": %d, \"move_list\": \"%s\"}\n",
+                pipe_name.c_str(), games, played, sec, visits, threads, batch,
+                lzb_engine::eager ? "eager" : "wait", ngpus, evals, evals / sec,
                 double(played) * visits / sec, s.batches,
-                s.batches ? double(s.positions) / s.batches : 0.0, s.timeouts);
+                s.batches ? double(s.positions) / s.batches : 0.0, s.timeouts, s.halted, checked,
+                move_list.c_str());
     return 0;
 }

@@ -38,8 +38,15 @@ def write_network(blocks, filters, seed, path):
     W.write_v1(raw, path)
 
 
-def run(blocks, filters, threads, batch, gpus, visits, moves, precision="fp16", seed=2004,
-        weights=None, verbose=True, timeout=3600, games=1, batching="eager"):
+def run(blocks, filters, threads, batch, gpus, visits, moves, precision="auto", seed=2004,
+        weights=None, verbose=True, timeout=3600, games=1, batching="eager", cpu_only=False,
+        selfchecks=0, deterministic=0, inject_half_init_failure=0):
+    """One engine_bench run; returns its summary line as a dict plus the moves
+    the engine answered over GTP and the text it logged ("log").  precision:
+    auto / single / half as the engine's --precision, or a mode name of the
+    library; cpu_only runs the reference's own CPUPipe (the engine's --cpu-only);
+    selfchecks forces that many of the engine's built-in GPU-against-CPU checks;
+    deterministic is a tree-size limit in bytes that makes the game repeatable."""
     if not os.path.exists(EXE):
         raise RuntimeError("%s is missing: make -C %s (needs the reference tree)" % (EXE, HERE))
     tmp = None
@@ -51,14 +58,24 @@ def run(blocks, filters, threads, batch, gpus, visits, moves, precision="fp16", 
     cmd = [EXE, "--weights", weights, "--threads", str(threads), "--batch", str(batch), "--gpus",
            str(gpus), "--visits", str(visits), "--moves", str(moves), "--precision", precision,
            "--games", str(games), "--batching", batching]
+    if cpu_only:
+        cmd.append("--cpu-only")
+    if selfchecks:
+        cmd += ["--selfchecks", str(selfchecks)]
+    if deterministic:
+        cmd += ["--deterministic", str(deterministic)]
+    if inject_half_init_failure:
+        cmd += ["--inject-half-init-failure", str(inject_half_init_failure)]
     if verbose and games == 1:
         cmd.append("--verbose")
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
+    env = dict(os.environ, OPENBLAS_NUM_THREADS="1")   # as the engine sets it (src/Network.cpp:498-499)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
     if tmp is not None:
         os.unlink(weights)
     if r.returncode != 0:
         raise RuntimeError("engine_bench failed (%d): %s" % (r.returncode, r.stderr[-2000:]))
     summary = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    summary["log"] = r.stderr
     summary["gtp_moves"] = re.findall(r"^= (\S+)", r.stdout, flags=re.M)
     # the engine's own per-move line: "<visits> visits, <nodes> nodes, <playouts> playouts, <n/s> n/s"
     rates = [(int(a), int(b)) for a, b in re.findall(r"(\d+) playouts, (\d+) n/s", r.stderr)]
@@ -81,8 +98,15 @@ if __name__ == "__main__":
                     help="games played at once in one process, sharing the pipe's queue")
     ap.add_argument("--batching", default="eager", choices=("eager", "wait"),
                     help="wait: the reference's full-batch-or-timeout rule; eager: take what is waiting")
-    ap.add_argument("--precision", default="fp16")
+    ap.add_argument("--precision", default="auto",
+                    help="auto, single, half (the engine's own choices) or a mode name: fp32, fp16, fp16x2, bf16 ...")
+    ap.add_argument("--cpu-only", action="store_true", help="the reference's CPUPipe instead of the GPU")
+    ap.add_argument("--selfchecks", type=int, default=0)
+    ap.add_argument("--deterministic", type=int, default=0, metavar="BYTES")
     ap.add_argument("--weights", default=None)
     a = ap.parse_args()
-    print(json.dumps(run(a.blocks, a.filters, a.threads, a.batch, a.gpus, a.visits, a.moves,
-                         a.precision, weights=a.weights, games=a.games, batching=a.batching)))
+    out = run(a.blocks, a.filters, a.threads, a.batch, a.gpus, a.visits, a.moves,
+              a.precision, weights=a.weights, games=a.games, batching=a.batching,
+              cpu_only=a.cpu_only, selfchecks=a.selfchecks, deterministic=a.deterministic)
+    out.pop("log")
+    print(json.dumps(out))

@@ -157,14 +157,21 @@ void CUDAPipe::forward(const std::vector<float>& input, std::vector<float>& outp
     auto entry = std::make_shared<Entry>(input, output_pol, output_val);
     {
         std::lock_guard<std::mutex> lk(m_mutex);
-        if (m_draining) throw NetworkHaltException();
+        if (m_draining) {
+            m_stats.halted++;
+            throw NetworkHaltException();
+        }
         if (m_live_gpus.load() == 0) throw std::runtime_error("CUDAPipe: no GPU left in service");
         m_queue.push_back(entry);
         // Requests arriving while a partial batch is in flight mean the wait
         // was too short (src/OpenCLScheduler.cpp:267-269).
         if (m_partial_in_progress.load() && m_wait_ms < kMaxWaitMs) m_wait_ms += 2;
     }
-    m_cv.notify_one();
+    // EAGER waiters have different wake conditions (room on their own GPU, the
+    // gathering window, a full batch), so one wake-up could land on a worker
+    // that goes back to sleep while an idle GPU's worker sleeps on.
+    if (m_batching == Batching::EAGER) m_cv.notify_all();
+    else m_cv.notify_one();
     std::unique_lock<std::mutex> lk(entry->mutex);
     entry->cv.wait(lk, [&] { return entry->done; });
     if (entry->halted) throw NetworkHaltException();
@@ -186,10 +193,11 @@ std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out, int gpu_index)
     const size_t full = static_cast<size_t>(m_batch_size);
     while (m_batching == Batching::EAGER) {
         m_cv.wait(lk, [&] {
-            return !m_running || (!m_queue.empty() && !m_gathering &&
-                                  (m_queue.size() >= full || m_in_flight[gpu_index] < 2));
+            return !m_running || m_gpu_failed[gpu_index] ||
+                   (!m_queue.empty() && !m_gathering &&
+                    (m_queue.size() >= full || m_in_flight[gpu_index] < 2));
         });
-        if (!m_running) return batch;
+        if (!m_running || m_gpu_failed[gpu_index]) return batch;
         // A lone caller (one request now, one in the previous batch) gains
         // nothing from the window; everybody else does.
         if (m_queue.size() < full && m_gather_us > 0 && (m_queue.size() > 1 || m_last_batch > 1)) {
@@ -197,7 +205,11 @@ std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out, int gpu_index)
             m_cv.wait_for(lk, std::chrono::microseconds(m_gather_us),
                           [&] { return !m_running || m_queue.size() >= full; });
             m_gathering = false;
-            if (!m_running) return batch;
+            if (!m_running || m_gpu_failed[gpu_index]) {
+                lk.unlock();
+                m_cv.notify_all();         // the window is closed: somebody else gathers
+                return batch;
+            }
         }
         count = std::min(m_queue.size(), full);
         if (count == 0) continue;          // drained while gathering
@@ -211,16 +223,17 @@ std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out, int gpu_index)
         return batch;
     }
     while (true) {
-        if (!m_running) return batch;
+        if (!m_running || m_gpu_failed[gpu_index]) return batch;
         count = m_queue.size();
         if (count >= static_cast<size_t>(m_batch_size)) {
             count = m_batch_size;
             break;
         }
-        const bool filled = m_cv.wait_for(lk, std::chrono::milliseconds(m_wait_ms), [this] {
-            return !m_running || m_queue.size() >= static_cast<size_t>(m_batch_size);
+        const bool filled = m_cv.wait_for(lk, std::chrono::milliseconds(m_wait_ms), [&] {
+            return !m_running || m_gpu_failed[gpu_index] ||
+                   m_queue.size() >= static_cast<size_t>(m_batch_size);
         });
-        if (!m_running) return batch;
+        if (!m_running || m_gpu_failed[gpu_index]) return batch;
         if (!filled && !m_queue.empty() && !m_partial_in_progress.exchange(true)) {
             if (m_wait_ms > 1) m_wait_ms--;
             count = std::min(m_queue.size(), static_cast<size_t>(m_batch_size));
@@ -233,7 +246,38 @@ std::vector<CUDAPipe::EntryPtr> CUDAPipe::pickup(bool* timed_out, int gpu_index)
     return batch;
 }
 
+// Takes a GPU out of rotation: its workers leave at their next look at the
+// queue (pickup wakes on the flag), and when it was the last GPU everybody
+// still queued is released with an error.
+void CUDAPipe::retire_gpu(int gpu_index, const std::string& error) {
+    std::deque<EntryPtr> orphans;
+    {
+        std::lock_guard<std::mutex> lk(m_mutex);
+        if (!m_gpu_failed[gpu_index]) {
+            m_gpu_failed[gpu_index] = 1;
+            if (--m_live_gpus <= 0) {
+                m_live_gpus = 0;
+                orphans.swap(m_queue);
+            }
+        }
+    }
+    m_cv.notify_all();
+    for (auto& e : orphans) finish(e, false, "no GPU left in service (" + error + ")");
+}
+
 void CUDAPipe::worker(int gpu_index, int slot) {
+    // Nothing may leave a thread body as an exception (that would end the
+    // process): a worker that cannot get its staging memory retires its GPU.
+    try {
+        serve(gpu_index, slot);
+    } catch (const std::exception& e) {
+        retire_gpu(gpu_index, e.what());
+    } catch (...) {
+        retire_gpu(gpu_index, "unknown exception in a worker");
+    }
+}
+
+void CUDAPipe::serve(int gpu_index, int slot) {
     // Staging buffers of this worker, released when it leaves.
     struct Staging {
         Backend* b;
@@ -247,20 +291,22 @@ void CUDAPipe::worker(int gpu_index, int slot) {
     Staging pol(m_backend.get(), static_cast<size_t>(m_batch_size) * kPolicyFloats);
     Staging val(m_backend.get(), static_cast<size_t>(m_batch_size) * kValueFloats);
     while (true) {
-        {
-            std::lock_guard<std::mutex> lk(m_mutex);
-            if (m_gpu_failed[gpu_index]) return;   // a sibling worker saw this GPU fail
-        }
         bool timed_out = false;
         auto batch = pickup(&timed_out, gpu_index);
-        if (batch.empty()) return;   // shutting down
+        if (batch.empty()) return;   // shutting down, or a sibling worker saw this GPU fail
         const int n = static_cast<int>(batch.size());
         for (int i = 0; i < n; i++) {
             std::memcpy(&in[static_cast<size_t>(i) * kInputFloats], batch[i]->in.data(),
                         sizeof(float) * kInputFloats);
         }
         std::string error;
-        const int rc = m_backend->forward(gpu_index, slot, in.data(), n, pol.data(), val.data(), &error);
+        int rc;
+        try {
+            rc = m_backend->forward(gpu_index, slot, in.data(), n, pol.data(), val.data(), &error);
+        } catch (const std::exception& e) {
+            rc = -1;
+            error = e.what();
+        }
         if (rc == 0) {
             for (int i = 0; i < n; i++) {
                 std::memcpy(batch[i]->out_p.data(), &pol[static_cast<size_t>(i) * kPolicyFloats],
@@ -283,20 +329,7 @@ void CUDAPipe::worker(int gpu_index, int slot) {
         if (m_batching == Batching::EAGER) m_cv.notify_all();   // room for another batch
         else if (timed_out) m_partial_in_progress = false;
         if (rc != 0) {
-            // This GPU leaves the rotation (its other workers stop at their
-            // next turn).  If it was the last one, wake everybody who waits.
-            std::deque<EntryPtr> orphans;
-            {
-                std::lock_guard<std::mutex> lk(m_mutex);
-                if (!m_gpu_failed[gpu_index]) {
-                    m_gpu_failed[gpu_index] = 1;
-                    if (--m_live_gpus <= 0) {
-                        m_live_gpus = 0;
-                        orphans.swap(m_queue);
-                    }
-                }
-            }
-            for (auto& e : orphans) finish(e, false, "no GPU left in service (" + error + ")");
+            retire_gpu(gpu_index, error);
             return;
         }
     }
@@ -318,6 +351,7 @@ void CUDAPipe::drain() {
         std::lock_guard<std::mutex> lk(m_mutex);
         m_draining = true;
         queued.swap(m_queue);
+        m_stats.halted += queued.size();
     }
     for (auto& e : queued) finish(e, true, "");
 }

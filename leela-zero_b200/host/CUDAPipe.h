@@ -76,6 +76,7 @@ public:
         std::size_t positions = 0;      // positions evaluated
         std::size_t full_batches = 0;   // calls that carried batch_size positions
         std::size_t timeouts = 0;       // calls sent because the wait ran out
+        std::size_t halted = 0;         // callers sent away with NetworkHaltException (drain)
         int wait_ms = 0;                // current wait for a full batch
     };
 
@@ -97,6 +98,7 @@ public:
 
     Stats stats() const;
     int live_gpus() const;
+    Precision precision() const { return m_precision; }
     // Call before push_weights.  gather_us: how long an EAGER worker lets
     // further requests join once the first one is there.
     void set_batching(Batching mode, int gather_us = 100);
@@ -122,6 +124,8 @@ private:
     using EntryPtr = std::shared_ptr<Entry>;
 
     void worker(int gpu_index, int slot);
+    void serve(int gpu_index, int slot);
+    void retire_gpu(int gpu_index, const std::string& error);
     std::vector<EntryPtr> pickup(bool* timed_out, int gpu_index);
     static void finish(const EntryPtr& e, bool halted, const std::string& error);
 

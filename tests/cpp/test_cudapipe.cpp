@@ -33,6 +33,8 @@ public:
     std::atomic<int> max_n{0};
     std::atomic<int> loaded_gpus{0};
     std::atomic<int> fail_gpu{-1};       // gpu index whose calls fail
+    std::atomic<int> throw_gpu{-1};      // gpu index whose calls throw
+    std::atomic<int> calls_on[4] = {{0}, {0}, {0}, {0}};
     std::atomic<int> delay_ms{0};
     std::atomic<bool> gate_closed{false};  // while true, forward() blocks
     std::atomic<int> running[4] = {{0}, {0}, {0}, {0}};   // calls inside forward(), per gpu
@@ -68,6 +70,8 @@ public:
         }
         int prev = max_n.load();
         while (n > prev && !max_n.compare_exchange_weak(prev, n)) {}
+        calls_on[gpu & 3]++;
+        if (gpu == throw_gpu) throw std::runtime_error("injected exception");
         if (gpu == fail_gpu) {
             *error = "injected failure";
             return 2;
@@ -360,7 +364,71 @@ static void test_eager_drain_failure_and_shutdown() {
     pipe.reset();                                 // workers idle in the eager wait must leave
 }
 
+static void test_failed_gpu_gets_no_further_batches() {
+    // Two GPUs with two workers each.  After GPU 0 fails once, its second
+    // worker, asleep in the queue wait at that moment, must leave without
+    // taking a batch: one failing backend call, one failed caller.
+    for (int eager = 0; eager < 2; eager++) {
+        FakeBackend* fb;
+        auto pipe = make_pipe(&fb, {0, 1}, 2, 8, eager != 0);
+        fb->fail_gpu = 0;
+        int errors = 0, ok = 0;
+        for (int r = 0; r < 60; r++) {
+            Caller c(r);
+            try {
+                pipe->forward(c.in, c.pol, c.val);
+                if (c.answer_is_mine()) ok++;
+            } catch (const std::runtime_error&) {
+                errors++;
+            }
+        }
+        CHECK(fb->calls_on[0] <= 1 && errors == fb->calls_on[0] && ok == 60 - errors);
+        CHECK(pipe->live_gpus() == (errors ? 1 : 2));
+    }
+}
+
+static void test_backend_exception_is_an_error_not_a_crash() {
+    FakeBackend* fb;
+    auto pipe = make_pipe(&fb, {0, 1}, 2, 4);
+    fb->throw_gpu = 1;
+    int errors = 0, ok = 0;
+    for (int r = 0; r < 40; r++) {
+        Caller c(r);
+        try {
+            pipe->forward(c.in, c.pol, c.val);
+            if (c.answer_is_mine()) ok++;
+        } catch (const std::runtime_error& e) {
+            errors++;
+            CHECK(std::string(e.what()).find("injected exception") != std::string::npos);
+        }
+    }
+    CHECK(errors <= 1 && ok == 40 - errors && pipe->live_gpus() == (errors ? 1 : 2));
+}
+
+static void test_halted_callers_are_counted() {
+    FakeBackend* fb;
+    auto pipe = make_pipe(&fb, {0}, 4, 8);
+    fb->gate_closed = true;
+    std::atomic<int> halted{0};
+    std::vector<std::thread> ts;
+    for (int t = 0; t < 12; t++) {
+        ts.emplace_back([&, t] {
+            Caller c(t);
+            try { pipe->forward(c.in, c.pol, c.val); } catch (const NetworkHaltException&) { halted++; }
+        });
+    }
+    std::this_thread::sleep_for(std::chrono::milliseconds(100));
+    pipe->drain();
+    fb->gate_closed = false;
+    for (auto& t : ts) t.join();
+    CHECK(halted >= 4 && pipe->stats().halted == static_cast<size_t>(halted.load()));
+    pipe->resume();
+}
+
 int main() {
+    test_failed_gpu_gets_no_further_batches();
+    test_backend_exception_is_an_error_not_a_crash();
+    test_halted_callers_are_counted();
     test_many_callers_two_gpus();
     test_single_caller_does_not_deadlock();
     test_partial_batch_takes_all_waiting();

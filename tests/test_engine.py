@@ -1,7 +1,11 @@
-"""The reference engine itself (UCTSearch, Network, NNCache, GTP: its sources
-compiled unchanged) playing on top of CUDAPipe: the drop-in check at the level
-a user of the engine sees.  The binary is built where the reference tree is
-present (leela-zero_b200/engine/Makefile) and travels with the repository."""
+"""The reference engine itself (UCTSearch, Network, NNCache, GTP, CPUPipe: its
+sources compiled unchanged as a GPU build) with CUDAPipe standing where its
+OpenCLScheduler stands: the drop-in check at the level a user of the engine
+sees.  Covers the engine's precision selection with its fall-back, its built-in
+self-check against its own CPUPipe, the stop-the-search protocol (drain and
+resume) and a move-by-move comparison of the engine on CPUPipe with the engine
+on CUDAPipe.  The binary is built where the reference tree is present
+(leela-zero_b200/engine/Makefile) and travels with the repository."""
 import importlib.util
 import os
 import re
@@ -62,14 +66,94 @@ int main() {
     assert r.returncode == 0, r.stdout
 
 
+def _engine():
+    run_engine = _runner()
+    if not os.path.exists(run_engine.EXE):
+        pytest.skip("engine_bench not built (needs the reference tree)")
+    return run_engine
+
+
+TREE_BYTES = 3000000     # stops each deterministic search after roughly 700 simulations
+
+
+def test_engine_on_cpupipe_is_repeatable():
+    """The deterministic mode (one seeded search thread, searches ended by the
+    tree-size limit) gives the same game twice; the comparison of two pipes
+    below rests on that.  Runs the reference's CPUPipe: no GPU needed."""
+    run_engine = _engine()
+    a = run_engine.run(blocks=2, filters=32, threads=1, batch=1, gpus=1, visits=0, moves=5,
+                       seed=2082, cpu_only=True, deterministic=TREE_BYTES)
+    b = run_engine.run(blocks=2, filters=32, threads=1, batch=1, gpus=1, visits=0, moves=5,
+                       seed=2082, cpu_only=True, deterministic=TREE_BYTES)
+    assert a["pipe"] == "CPUPipe" and a["moves"] == 5
+    assert a["move_list"] == b["move_list"] and a["engine_playouts"] == b["engine_playouts"]
+
+
+@pytest.mark.gpu
+def test_engine_on_cudapipe_plays_the_same_game_as_on_cpupipe():
+    """Same weights, same seed, one search thread: the engine on CUDAPipe in
+    fp32 plays the moves the engine on its own CPUPipe plays, with the same
+    number of playouts (12 moves, about 700 simulations each)."""
+    run_engine = _engine()
+    kw = dict(blocks=2, filters=32, threads=1, batch=1, gpus=1, visits=0, moves=12, seed=2082,
+              deterministic=TREE_BYTES)
+    cpu = run_engine.run(cpu_only=True, **kw)
+    gpu = run_engine.run(precision="single", **kw)
+    assert cpu["pipe"] == "CPUPipe" and gpu["pipe"] == "CUDAPipe fp32"
+    assert gpu["nn_evals"] > 12 * 100
+    assert gpu["move_list"] == cpu["move_list"], (gpu["move_list"], cpu["move_list"])
+    assert gpu["engine_playouts"] == cpu["engine_playouts"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("precision,pipe", [("single", "CUDAPipe fp32"), ("auto", "CUDAPipe fp16x2"),
+                                            ("fp16", "CUDAPipe fp16"), ("bf16", "CUDAPipe bf16")])
+def test_engine_self_check_passes(precision, pipe):
+    """The engine's own comparison of its GPU pipe with its CPUPipe
+    (Network::compare_net_outputs, src/Network.cpp:667-690), forced after each
+    of 8 moves on a 6 x 64 network; with precision auto the engine's
+    select_precision also runs it once while choosing (src/Network.cpp:426-431)."""
+    run_engine = _engine()
+    out = run_engine.run(blocks=6, filters=64, threads=2, batch=2, gpus=1, visits=40, moves=8,
+                         precision=precision, seed=2083, selfchecks=8)
+    assert out["pipe"] == pipe
+    assert out["selfchecks_passed"] == 8 and out["moves"] == 8
+    if precision == "auto":
+        assert "using fp16/half or tensor core compute support" in out["log"]
+        assert "Falling back" not in out["log"]
+
+
+@pytest.mark.gpu
+def test_half_precision_failure_falls_back_to_single():
+    """A half-precision pipe that refuses to initialise (injected on the host)
+    is replaced by the single-precision one, as the engine does for OpenCL
+    (src/Network.cpp:426-441), and the game goes on."""
+    run_engine = _engine()
+    out = run_engine.run(blocks=2, filters=32, threads=2, batch=2, gpus=1, visits=40, moves=4,
+                         precision="auto", seed=2084, selfchecks=2, inject_half_init_failure=1)
+    assert "Falling back to single precision" in out["log"]
+    assert out["pipe"] == "CUDAPipe fp32" and out["moves"] == 4 and out["selfchecks_passed"] == 2
+
+
+@pytest.mark.gpu
+def test_search_end_halts_queued_callers():
+    """UCTSearch::think ends a search with drain_evals / resume_evals
+    (src/UCTSearch.cpp:829-832).  Through the engine that must reach
+    CUDAPipe::drain: search threads still queued for a batch leave with
+    NetworkHaltException (counted by the pipe) and the next search runs."""
+    run_engine = _engine()
+    out = run_engine.run(blocks=2, filters=32, threads=8, batch=8, gpus=1, visits=150, moves=10,
+                         precision="half", seed=2085, batching="wait")
+    assert out["moves"] == 10 and out["halted"] > 0
+    assert out["nn_evals"] >= 10 * 50
+
+
 @pytest.mark.gpu
 def test_engine_plays_on_cudapipe():
     """A short game: 4 search threads, 100 visits per move.  The engine must
     produce legal GTP moves and every evaluation must have gone through the
     pipe in batches."""
-    run_engine = _runner()
-    if not os.path.exists(run_engine.EXE):
-        pytest.skip("engine_bench not built (needs the reference tree)")
+    run_engine = _engine()
     out = run_engine.run(blocks=2, filters=32, threads=4, batch=4, gpus=1, visits=100, moves=8,
                          precision="fp16", seed=2080)
     assert out["moves"] == 8 and len(out["gtp_moves"]) == 8
@@ -85,9 +169,7 @@ def test_concurrent_games_share_the_queue():
     """Six games at once, two search threads each, one network: all games
     finish their moves and the batches are larger than one tree's two callers
     could make them."""
-    run_engine = _runner()
-    if not os.path.exists(run_engine.EXE):
-        pytest.skip("engine_bench not built (needs the reference tree)")
+    run_engine = _engine()
     out = run_engine.run(blocks=2, filters=32, threads=2, batch=12, gpus=1, visits=60, moves=6,
                          precision="fp16", seed=2081, games=6, batching="eager")
     assert out["games"] == 6 and out["moves"] == 36

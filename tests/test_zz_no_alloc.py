@@ -1,13 +1,14 @@
 """lzb_conv3x3_static: the entry point for callers that cannot allocate device
 memory (hosts that own all of it through their own pool, threads that must not
 take cudaMalloc's device-wide synchronisation).  It keeps its working memory in
-a fixed array inside the library, so this test checks three things through the
+a fixed array inside the library, so this test checks four things through the
 C ABI: that it agrees with the allocating entry point (lzb_ctx_debug_conv of an
-fp32 pipe) on the same layer, that a second call right after the first is not
-disturbed by what the first left in the shared array (the second call is
-smaller and uses other channel counts), and that sizes beyond the stated
-limits are refused.  Tolerance: 2e-6 of the largest output, the bound the
-single-layer fp32 tests use.
+fp32 pipe) on the same layer, that both agree with the CPU restatement of the
+reference's layer (the checker the other parity tests use), that a second call
+right after the first is not disturbed by what the first left in the shared
+array (the second call is smaller and uses other channel counts), and that
+sizes beyond the stated limits are refused.  Tolerance: 2e-6 of the largest
+output, the bound the single-layer fp32 tests use.
 
 This file is collected last on purpose: a run that stops at the first failure
 has then already run every other test."""
@@ -46,7 +47,28 @@ def _static_layer(lzb, net, layer, x, residual=None):
     return d_out.cpu().numpy()
 
 
-def test_static_entry_point_matches_allocating_one(lzb):
+def _cpu_layer(oracle, net, layer, x, res=None):
+    """The layer on the CPU: input transform, 36 contractions, output
+    transform, batch-norm [+ residual] + ReLU, stage by stage as CPUPipe runs
+    them (src/CPUPipe.cpp:63-284, 352-377)."""
+    lib = oracle.port_lib()
+    U = net["U"][layer]
+    cin, C = U.shape[1], U.shape[2]
+    out = np.empty((x.shape[0], C, 361), np.float32)
+    V = np.empty((36, cin, 25), np.float32)
+    M = np.empty((36, C, 25), np.float32)
+    for i in range(x.shape[0]):
+        xi = np.ascontiguousarray(x[i].reshape(cin, 361))
+        lib.lzo_transform_in(oracle._ptr(xi), oracle._ptr(V), cin)
+        lib.lzo_sgemm36(oracle._ptr(U), oracle._ptr(V), oracle._ptr(M), cin, C)
+        lib.lzo_transform_out(oracle._ptr(M), oracle._ptr(out[i]), C)
+        r = None if res is None else oracle._ptr(np.ascontiguousarray(res[i]))
+        lib.lzo_batchnorm(C, 361, oracle._ptr(out[i]), oracle._ptr(net["bn_mean"][layer]),
+                          oracle._ptr(net["bn_invstd"][layer]), r)
+    return out
+
+
+def test_static_entry_point_matches_allocating_one(lzb, oracle):
     W = lzb.weights
     net = W.synthetic_network(1, 64, 4000)
     small = W.synthetic_network(1, 24, 4001)
@@ -60,6 +82,8 @@ def test_static_entry_point_matches_allocating_one(lzb):
     want = ctx.debug_conv(2, a1, a0)
     got = _static_layer(lzb, net, 2, a1, a0)
     assert np.abs(got - want).max() <= REL * max(1.0, np.abs(want).max())
+    cpu = _cpu_layer(oracle, net, 2, a1, a0)
+    assert np.abs(got - cpu).max() <= REL * max(1.0, np.abs(cpu).max())
 
     # call 2, straight after: fewer positions, 18 -> 24 channels, no residual;
     # the array still holds call 1's tiles, weights and batch-norm vectors
@@ -67,6 +91,8 @@ def test_static_entry_point_matches_allocating_one(lzb):
     want2 = ctx_small.debug_conv(0, x2)
     got2 = _static_layer(lzb, small, 0, x2)
     assert np.abs(got2 - want2).max() <= REL * max(1.0, np.abs(want2).max())
+    cpu2 = _cpu_layer(oracle, small, 0, x2)
+    assert np.abs(got2 - cpu2).max() <= REL * max(1.0, np.abs(cpu2).max())
 
     # and once more the first case, to see that call 2 left nothing behind either
     got3 = _static_layer(lzb, net, 2, a1, a0)
