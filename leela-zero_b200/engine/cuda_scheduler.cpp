@@ -15,6 +15,7 @@ bool eager = true;
 int callers = 0;
 int fail_half_init = 0;
 CUDAPipe* last_pipe = nullptr;
+std::unique_ptr<CUDAPipe::Backend> (*backend_factory)() = nullptr;
 std::atomic<unsigned long long> evals{0};
 
 namespace {

@@ -29,6 +29,7 @@
 #include "config.h"
 
 #include <atomic>
+#include <memory>
 #include <stdexcept>
 #include <vector>
 
@@ -43,6 +44,9 @@ extern bool eager;                        // CUDAPipe::Batching::EAGER instead o
 extern int callers;                       // threads that will call forward(); 0: cfg_num_threads
 extern int fail_half_init;                // test hook: the next N half-precision pipes refuse to initialise
 extern CUDAPipe* last_pipe;               // the pipe constructed last (statistics)
+// Test hook: when set, makes the backend of every pipe constructed (a fake one,
+// to drive the engine's precision selection and stop protocol without a GPU).
+extern std::unique_ptr<CUDAPipe::Backend> (*backend_factory)();
 extern std::atomic<unsigned long long> evals;   // forward() calls on GPU pipes
 CUDAPipe::Precision precision_from_name(const char* name, bool* ok);
 void note_pipe(CUDAPipe* pipe, bool alive);
@@ -65,7 +69,9 @@ public:
     OpenCLScheduler()
         : CUDAPipe(cfg_gpus, static_cast<int>(cfg_batch_size),
                    lzb_engine::callers > 0 ? lzb_engine::callers : static_cast<int>(cfg_num_threads),
-                   is_half ? lzb_engine::half_mode : lzb_engine::single_mode) {
+                   is_half ? lzb_engine::half_mode : lzb_engine::single_mode,
+                   lzb_engine::backend_factory ? lzb_engine::backend_factory()
+                                               : std::unique_ptr<CUDAPipe::Backend>()) {
         if (lzb_engine::eager) set_batching(Batching::EAGER);
         lzb_engine::note_pipe(this, true);
     }

@@ -59,6 +59,19 @@
 #include "cuda_scheduler.h"
 
 namespace {
+// The network of the many-games mode.  Every search ends with drain_evals /
+// resume_evals (src/UCTSearch.cpp:829-832), which stops ALL evaluations of the
+// network: right for the engine's one search at a time, wrong when other games
+// are in the middle of their searches on the same network (their search
+// threads would leave and those searches would never finish).  Both calls are
+// virtual in the engine (src/Network.h:114-117); here they do nothing, and the
+// threads of a finished search return when their current batch does.
+class SharedNetwork : public Network {
+public:
+    void drain_evals() override {}
+    void resume_evals() override {}
+};
+
 // N games at once on one shared network; returns the number of moves played.
 int play_games(Network& network, int games, int moves) {
     std::vector<std::unique_ptr<GameState>> states;
@@ -169,7 +182,7 @@ int main(int argc, char** argv) {
         tg.add_task([] { Random::get_Rng().seedrandom(12345); });
         tg.wait_all();
     }
-    auto network = std::make_unique<Network>();
+    std::unique_ptr<Network> network(games > 1 ? new SharedNetwork : new Network);
     Network* net = network.get();
     try {
         // the cache is sized from the playout limit (src/Network.cpp:578-587); N games share it

@@ -21,6 +21,8 @@ import tempfile
 HERE = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(HERE)
 EXE = os.path.join(HERE, "_build", "engine_bench")
+# the same engine with the reference's CPUPipe behind the scheduler: the checker of the engine tests
+EXE_CHECK = os.path.join(HERE, "_build", "engine_check")
 
 
 def _weights_module():
@@ -39,23 +41,24 @@ def write_network(blocks, filters, seed, path):
 
 
 def run(blocks, filters, threads, batch, gpus, visits, moves, precision="auto", seed=2004,
-        weights=None, verbose=True, timeout=3600, games=1, batching="eager", cpu_only=False,
-        selfchecks=0, deterministic=0, inject_half_init_failure=0):
+        weights=None, verbose=True, timeout=600, games=1, batching="eager", cpu_only=False,
+        selfchecks=0, deterministic=0, inject_half_init_failure=0, exe=None):
     """One engine_bench run; returns its summary line as a dict plus the moves
     the engine answered over GTP and the text it logged ("log").  precision:
     auto / single / half as the engine's --precision, or a mode name of the
     library; cpu_only runs the reference's own CPUPipe (the engine's --cpu-only);
     selfchecks forces that many of the engine's built-in GPU-against-CPU checks;
     deterministic is a tree-size limit in bytes that makes the game repeatable."""
-    if not os.path.exists(EXE):
-        raise RuntimeError("%s is missing: make -C %s (needs the reference tree)" % (EXE, HERE))
+    exe = exe or EXE
+    if not os.path.exists(exe):
+        raise RuntimeError("%s is missing: make -C %s (needs the reference tree)" % (exe, HERE))
     tmp = None
     if weights is None:
         tmp = tempfile.NamedTemporaryFile(suffix=".txt.gz", delete=False)
         tmp.close()
         weights = tmp.name
         write_network(blocks, filters, seed, weights)
-    cmd = [EXE, "--weights", weights, "--threads", str(threads), "--batch", str(batch), "--gpus",
+    cmd = [exe, "--weights", weights, "--threads", str(threads), "--batch", str(batch), "--gpus",
            str(gpus), "--visits", str(visits), "--moves", str(moves), "--precision", precision,
            "--games", str(games), "--batching", batching]
     if cpu_only:

@@ -80,7 +80,7 @@ CUDAPipe::CUDAPipe(std::vector<int> gpus, int batch_size, int num_threads, Preci
       m_batch_size(std::max(1, batch_size)),
       m_num_threads(std::max(1, num_threads)),
       m_precision(precision),
-      m_backend(std::move(backend)) {
+      m_backend(backend ? std::move(backend) : std::unique_ptr<Backend>(new LzbBackend)) {
     // An empty list means "pick one" in the engine (src/OpenCLScheduler.cpp:90-94).
     if (m_gpus.empty()) m_gpus.push_back(0);
 }

@@ -84,6 +84,7 @@ public:
     // num_threads = cfg_num_threads (sizes the worker pool like the reference).
     CUDAPipe(std::vector<int> gpus, int batch_size, int num_threads,
              Precision precision = Precision::FP16);
+    // backend: what runs the batches; null selects the production backend.
     CUDAPipe(std::vector<int> gpus, int batch_size, int num_threads, Precision precision,
              std::unique_ptr<Backend> backend);
     ~CUDAPipe() override;

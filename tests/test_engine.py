@@ -76,31 +76,56 @@ def _engine():
 TREE_BYTES = 3000000     # stops each deterministic search after roughly 700 simulations
 
 
-def test_engine_on_cpupipe_is_repeatable():
+def test_engine_with_cpupipe_behind_the_scheduler_is_repeatable():
     """The deterministic mode (one seeded search thread, searches ended by the
     tree-size limit) gives the same game twice; the comparison of two pipes
-    below rests on that.  Runs the reference's CPUPipe: no GPU needed."""
+    below rests on that.  engine_check is the engine built as for the GPU, with
+    the reference's CPUPipe doing the arithmetic behind CUDAPipe's queue
+    (tests/cpp/engine_cpupipe_backend.cpp): no GPU needed.  The engine's own
+    --cpu-only run is repeatable too, but plays another game: without a GPU
+    pipe the engine draws no self-check lots from the random generator
+    (src/Network.cpp:786-788), so the random symmetries differ."""
     run_engine = _engine()
-    a = run_engine.run(blocks=2, filters=32, threads=1, batch=1, gpus=1, visits=0, moves=5,
-                       seed=2082, cpu_only=True, deterministic=TREE_BYTES)
-    b = run_engine.run(blocks=2, filters=32, threads=1, batch=1, gpus=1, visits=0, moves=5,
-                       seed=2082, cpu_only=True, deterministic=TREE_BYTES)
-    assert a["pipe"] == "CPUPipe" and a["moves"] == 5
+    kw = dict(blocks=2, filters=32, threads=1, batch=1, gpus=1, visits=0, moves=4, seed=2082,
+              deterministic=TREE_BYTES)
+    a = run_engine.run(precision="single", exe=run_engine.EXE_CHECK, **kw)
+    b = run_engine.run(precision="single", exe=run_engine.EXE_CHECK, **kw)
+    assert a["moves"] == 4 and a["nn_evals"] > 4 * 100
     assert a["move_list"] == b["move_list"] and a["engine_playouts"] == b["engine_playouts"]
+    c = run_engine.run(cpu_only=True, **kw)
+    d = run_engine.run(cpu_only=True, **kw)
+    assert c["pipe"] == "CPUPipe" and c["move_list"] == d["move_list"]
+
+
+def test_precision_selection_and_fall_back_without_a_gpu():
+    """Network::select_precision on the stand-in scheduler, with the CPUPipe
+    checker as backend: auto takes the half-precision pipe without a timing run
+    and checks it once against the CPU pipe; when that pipe refuses to
+    initialise the engine falls back to single precision
+    (src/Network.cpp:426-441)."""
+    run_engine = _engine()
+    kw = dict(blocks=2, filters=32, threads=2, batch=2, gpus=1, visits=30, moves=3, seed=2084,
+              exe=run_engine.EXE_CHECK, precision="auto", selfchecks=2)
+    ok = run_engine.run(**kw)
+    assert "using fp16/half or tensor core compute support" in ok["log"]
+    assert "Falling back" not in ok["log"] and ok["pipe"] == "CUDAPipe fp16x2"
+    fb = run_engine.run(inject_half_init_failure=1, **kw)
+    assert "Falling back to single precision" in fb["log"]
+    assert fb["pipe"] == "CUDAPipe fp32" and fb["moves"] == 3 and fb["selfchecks_passed"] == 2
 
 
 @pytest.mark.gpu
 def test_engine_on_cudapipe_plays_the_same_game_as_on_cpupipe():
-    """Same weights, same seed, one search thread: the engine on CUDAPipe in
-    fp32 plays the moves the engine on its own CPUPipe plays, with the same
+    """Same weights, same seed, one search thread, the engine's own precision
+    setting "single": the engine with CUDAPipe's fp32 kernels plays the moves
+    it plays with the reference's CPUPipe behind the same queue, with the same
     number of playouts (12 moves, about 700 simulations each)."""
     run_engine = _engine()
     kw = dict(blocks=2, filters=32, threads=1, batch=1, gpus=1, visits=0, moves=12, seed=2082,
-              deterministic=TREE_BYTES)
-    cpu = run_engine.run(cpu_only=True, **kw)
-    gpu = run_engine.run(precision="single", **kw)
-    assert cpu["pipe"] == "CPUPipe" and gpu["pipe"] == "CUDAPipe fp32"
-    assert gpu["nn_evals"] > 12 * 100
+              deterministic=TREE_BYTES, precision="single")
+    cpu = run_engine.run(exe=run_engine.EXE_CHECK, **kw)
+    gpu = run_engine.run(**kw)
+    assert gpu["pipe"] == "CUDAPipe fp32" and gpu["nn_evals"] > 12 * 100
     assert gpu["move_list"] == cpu["move_list"], (gpu["move_list"], cpu["move_list"])
     assert gpu["engine_playouts"] == cpu["engine_playouts"]
 
