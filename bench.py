@@ -266,6 +266,56 @@ def config2_sweep(pkg, W, torch, dev, device_index, precision):
             "precision": precision, "rows": rows}
 
 
+def scheduler_level(pkg, W, net, precision, gpus, seconds=2.0, block=64, callers_per_gpu=16):
+    """Evaluations/s through the product's own multi-GPU component: ONE process,
+    one CUDAPipe (one queue, worker threads per GPU, a full replica of the
+    network on every GPU), fed by caller threads that each hand in blocks of
+    `block` positions from ordinary (pageable) memory and get the raw head
+    planes back, batches of BATCH positions per GPU.  Everything a scheduler
+    does is inside the measured time: queueing, batch forming, packing the
+    planes into the staging buffers, copies to and from the GPUs, waking the
+    callers.  Wall clock over `seconds` after half a second of warm-up."""
+    import threading
+    import numpy as np
+    callers = max(32, callers_per_gpu * len(gpus))
+    sched = pkg.Scheduler(net, precision, gpus=tuple(gpus), batch_size=BATCH, num_threads=callers,
+                          eager=True)
+    done = [0] * callers
+    stop = threading.Event()
+    failures = []
+
+    def caller(t):
+        x = W.synthetic_positions(block, INPUT_SEED + 100 + t).reshape(block, -1)
+        pol = np.empty((block, 2, 361), np.float32)
+        val = np.empty((block, 361), np.float32)
+        try:
+            while not stop.is_set():
+                sched.forward(x, pol, val)
+                done[t] += block
+        except Exception as e:   # reported, never swallowed
+            failures.append(repr(e))
+
+    ts = [threading.Thread(target=caller, args=(t,)) for t in range(callers)]
+    [t.start() for t in ts]
+    time.sleep(0.5)
+    s0, c0, t0 = sched.stats(), sum(done), time.perf_counter()
+    time.sleep(seconds)
+    s1, c1, t1 = sched.stats(), sum(done), time.perf_counter()
+    stop.set()
+    [t.join() for t in ts]
+    sched.close()
+    if failures:
+        raise RuntimeError("scheduler_level: " + failures[0])
+    batches = s1["batches"] - s0["batches"]
+    return {"value": (c1 - c0) / (t1 - t0), "unit": "positions/s", "gpus": len(gpus),
+            "seconds": t1 - t0, "callers": callers, "positions_per_call": block,
+            "mean_batch": (s1["positions"] - s0["positions"]) / max(batches, 1),
+            "bit_plane_batches": s1["bit_plane_batches"] - s0["bit_plane_batches"], "batches": batches,
+            "note": "one process, CUDAPipe (C++ scheduler) over all GPUs of the job, callers' positions in "
+                    "pageable memory, fp32 planes in and raw head planes out as ForwardPipe::forward "
+                    "defines them; the other ranks are idle meanwhile"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -279,6 +329,8 @@ def main():
                     help="skip the extra timing of the plain fp16 mode")
     ap.add_argument("--no-sweep", action="store_true",
                     help="skip the batch sweep of the 20-block network (config 2)")
+    ap.add_argument("--no-scheduler-level", action="store_true",
+                    help="skip the measurement through the one-process scheduler (CUDAPipe)")
     ap.add_argument("--precision", default=PRECISION,
                     choices=["fp16", "bf16", "fp16-winograd", "bf16-winograd", "fp32", "fp16x2", "fp16x3"])
     args = ap.parse_args()
@@ -294,6 +346,9 @@ def main():
         import torch.distributed as dist
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # ranks other than 0 wait on the host (not in a GPU kernel) while rank 0 measures the
+        # one-process scheduler over all GPUs at the end
+        host_group = dist.new_group(backend="gloo")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
 
@@ -490,8 +545,13 @@ def main():
             out["cpu_baseline"] = {"value": rate, "unit": "positions/s", "cores": threads, "kind": kind,
                                    "sample": "%d positions of the same network, %d threads, %.1f s"
                                              % (npos, threads, dt)}
+        if args.precision == PRECISION and not args.no_scheduler_level:
+            ctx.close()
+            pipe.close()
+            out["scheduler_level"] = scheduler_level(pkg, W, net, args.precision, range(world))
         print(json.dumps(out), flush=True)
     if world > 1:
+        dist.barrier(group=host_group)
         dist.barrier()
         dist.destroy_process_group()
 

@@ -286,3 +286,106 @@ class Context:
             self.close()
         except Exception:
             pass
+
+
+# ---------------------------------------------------------------------------
+# The batching scheduler (C++ CUDAPipe) through its C view, include/lzb200_sched.h
+# ---------------------------------------------------------------------------
+
+SCHED_LIB_PATH = os.path.join(HERE, "libcudapipe.so")
+SCHED_SYMBOLS = (
+    "lzb_sched_last_error", "lzb_sched_create", "lzb_sched_destroy", "lzb_sched_add_conv",
+    "lzb_sched_start", "lzb_sched_forward", "lzb_sched_drain", "lzb_sched_resume", "lzb_sched_stats",
+)
+_sched_lib = None
+
+
+class SchedulerHalted(RuntimeError):
+    """The pipe is draining (NetworkHaltException in the C++ class)."""
+
+
+def sched_lib():
+    """Load libcudapipe.so (raises if it was not built)."""
+    global _sched_lib
+    if _sched_lib is None:
+        if not os.path.exists(SCHED_LIB_PATH):
+            raise RuntimeError("%s is missing: run `python leela-zero_b200/build.py`" % SCHED_LIB_PATH)
+        lib()   # liblzb200.so first: libcudapipe.so links against it
+        L = ctypes.CDLL(SCHED_LIB_PATH)
+        vp = ctypes.c_void_p
+        L.lzb_sched_last_error.restype = ctypes.c_char_p
+        L.lzb_sched_create.argtypes = [ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_int)] + [ctypes.c_int] * 5
+        L.lzb_sched_destroy.argtypes = [vp]
+        L.lzb_sched_destroy.restype = None
+        L.lzb_sched_add_conv.argtypes = [vp, _f32p, ctypes.c_int, ctypes.c_int, _f32p, _f32p]
+        L.lzb_sched_start.argtypes = [vp, ctypes.c_int, _f32p, _f32p]
+        L.lzb_sched_forward.argtypes = [vp, vp, ctypes.c_int, vp, vp]
+        L.lzb_sched_drain.argtypes = [vp]
+        L.lzb_sched_resume.argtypes = [vp]
+        L.lzb_sched_stats.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong)]
+        _sched_lib = L
+    return _sched_lib
+
+
+class Scheduler:
+    """CUDAPipe: one queue in front of a network replica on each of ``gpus``.
+
+    ``forward(x)`` blocks until its positions are evaluated and may be called
+    from any number of threads; positions of different callers share batches.
+    Returns the raw 1x1 head planes ``pol[n][2][361]``, ``val[n][361]`` like
+    ``ForwardPipe::forward``."""
+
+    def __init__(self, net, precision="fp16x2", gpus=(0,), batch_size=256, num_threads=64, eager=True):
+        L = sched_lib()
+        self._h = ctypes.c_void_p()
+        ids = (ctypes.c_int * len(gpus))(*gpus)
+        self._check(L.lzb_sched_create(ctypes.byref(self._h), ids, len(gpus), batch_size, num_threads,
+                                       PRECISIONS[precision], 1 if eager else 0))
+        channels = int(net["U"][0].shape[2])
+        for U, mean, inv in zip(net["U"], net["bn_mean"], net["bn_invstd"]):
+            U = np.ascontiguousarray(U, np.float32)
+            self._check(L.lzb_sched_add_conv(self._h, _ptr(U), U.shape[1], U.shape[2],
+                                             _ptr(np.ascontiguousarray(mean, np.float32)),
+                                             _ptr(np.ascontiguousarray(inv, np.float32))))
+        self._check(L.lzb_sched_start(self._h, channels,
+                                      _ptr(np.ascontiguousarray(net["pol_w"], np.float32)),
+                                      _ptr(np.ascontiguousarray(net["val_w"], np.float32))))
+
+    @staticmethod
+    def _check(code):
+        if code == 2:
+            raise SchedulerHalted(sched_lib().lzb_sched_last_error().decode())
+        if code != 0:
+            raise RuntimeError("CUDAPipe: " + sched_lib().lzb_sched_last_error().decode())
+
+    def forward(self, x, pol=None, val=None):
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, IN_FLOATS)
+        n = x.shape[0]
+        pol = np.empty((n, 2, 361), np.float32) if pol is None else pol
+        val = np.empty((n, 361), np.float32) if val is None else val
+        self._check(sched_lib().lzb_sched_forward(self._h, x.ctypes.data, n, pol.ctypes.data, val.ctypes.data))
+        return pol, val
+
+    def drain(self):
+        self._check(sched_lib().lzb_sched_drain(self._h))
+
+    def resume(self):
+        self._check(sched_lib().lzb_sched_resume(self._h))
+
+    def stats(self):
+        out = (ctypes.c_ulonglong * 8)()
+        self._check(sched_lib().lzb_sched_stats(self._h, out))
+        keys = ("batches", "positions", "full_batches", "timeouts", "bit_plane_batches", "halted",
+                "live_gpus", "wait_ms")
+        return dict(zip(keys, (int(v) for v in out)))
+
+    def close(self):
+        if self._h:
+            sched_lib().lzb_sched_destroy(self._h)
+            self._h = ctypes.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

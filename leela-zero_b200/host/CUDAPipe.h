@@ -62,6 +62,17 @@ public:
         // pol [n][2*361], val [n][361].  Returns 0 or an error code and text.
         virtual int forward(int gpu_index, int worker, const float* in, int n, float* pol,
                             float* val, std::string* error) = 0;
+        // Optional second form of the input: the 18 planes of a position as
+        // bits ([18][12] 32-bit words, bit i of word w = cell 32 w + i), which
+        // is what the engine's planes are (zeros and ones only,
+        // src/Network.cpp:935-966) and 30 times less to send to the GPU.  A
+        // backend that returns true from takes_bit_planes() gets a batch this
+        // way whenever every value of the batch is exactly 0 or 1.
+        virtual bool takes_bit_planes() const { return false; }
+        virtual int forward_bit_planes(int /*gpu_index*/, int /*worker*/, const unsigned int* /*planes*/,
+                                       int /*n*/, float* /*pol*/, float* /*val*/, std::string* /*error*/) {
+            return -1;
+        }
         // Staging memory for a worker's batches (page-locked in the production
         // backend); the default is ordinary memory.
         virtual float* alloc_staging(std::size_t floats) { return new float[floats]; }
@@ -76,6 +87,7 @@ public:
         std::size_t positions = 0;      // positions evaluated
         std::size_t full_batches = 0;   // calls that carried batch_size positions
         std::size_t timeouts = 0;       // calls sent because the wait ran out
+        std::size_t bit_plane_batches = 0;   // calls whose input went to the GPU as bit planes
         std::size_t halted = 0;         // callers sent away with NetworkHaltException (drain)
         int wait_ms = 0;                // current wait for a full batch
     };
@@ -97,6 +109,15 @@ public:
     void drain() override;
     void resume() override;
 
+    // Batched form of forward() for callers that hold several positions at
+    // once (many games in one process, benchmark drivers): n positions,
+    // in [n][18*361], pol [n][2*361], val [n][361], any host memory.  Blocks
+    // until all n are evaluated; the positions join the same queue as single
+    // requests and may be spread over several batches and GPUs.  Throws like
+    // forward().  Not part of ForwardPipe: the engine's interface carries one
+    // position per call (src/ForwardPipe.h:62-64).
+    void forward_many(const float* in, int n, float* pol, float* val);
+
     Stats stats() const;
     int live_gpus() const;
     Precision precision() const { return m_precision; }
@@ -104,31 +125,38 @@ public:
     // further requests join once the first one is there.
     void set_batching(Batching mode, int gather_us = 100);
 
+    static constexpr int kPlaneWords = 12;            // 361 cells as bits
+    static constexpr int kPackedWords = 18 * kPlaneWords;
     static constexpr int kInputFloats = 18 * 361;
     static constexpr int kPolicyFloats = 2 * 361;
     static constexpr int kValueFloats = 361;
     static constexpr int kMaxWaitMs = 100;
 
 private:
+    // One blocked caller: `count` positions in the caller's own memory.  The
+    // entry lives on the caller's stack; a worker touches it for the last time
+    // when it sets `done` (and notifies) under the entry's mutex.
     struct Entry {
-        const std::vector<float>& in;
-        std::vector<float>& out_p;
-        std::vector<float>& out_v;
+        const float* in;
+        const unsigned int* bits = nullptr;   // the same positions as bit planes, if all values are 0 or 1
+        float* out_p;
+        float* out_v;
+        int count;
         std::mutex mutex;
         std::condition_variable cv;
         bool done = false;
         bool halted = false;
         std::string error;
-        Entry(const std::vector<float>& i, std::vector<float>& p, std::vector<float>& v)
-            : in(i), out_p(p), out_v(v) {}
+        Entry(const float* i, int n, float* p, float* v) : in(i), out_p(p), out_v(v), count(n) {}
     };
-    using EntryPtr = std::shared_ptr<Entry>;
 
+    void submit_and_wait(Entry* const* entries, int n_entries);
     void worker(int gpu_index, int slot);
     void serve(int gpu_index, int slot);
     void retire_gpu(int gpu_index, const std::string& error);
-    std::vector<EntryPtr> pickup(bool* timed_out, int gpu_index);
-    static void finish(const EntryPtr& e, bool halted, const std::string& error);
+    std::vector<Entry*> pickup(bool* timed_out, int gpu_index);
+    std::vector<Entry*> take(std::size_t positions);
+    static void finish(Entry* e, bool halted, const std::string& error);
 
     std::vector<int> m_gpus;
     int m_batch_size;
@@ -137,10 +165,12 @@ private:
     std::unique_ptr<Backend> m_backend;
     int m_channels = 0;
     int m_workers_per_gpu = 1;
+    bool m_bit_planes = false;          // the backend takes positions as bit planes
 
     mutable std::mutex m_mutex;
     std::condition_variable m_cv;
-    std::deque<EntryPtr> m_queue;
+    std::deque<Entry*> m_queue;
+    std::size_t m_queued = 0;            // positions in m_queue
     bool m_running = true;
     std::atomic<bool> m_draining{false};
     std::atomic<bool> m_partial_in_progress{false};

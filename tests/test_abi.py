@@ -8,8 +8,8 @@ import pytest
 from conftest import ROOT
 
 
-def _declared():
-    text = open(os.path.join(ROOT, "include", "lzb200.h")).read()
+def _declared(header="lzb200.h"):
+    text = open(os.path.join(ROOT, "include", header)).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(lzb_[a-z0-9_]+)\s*\(", text)))
 
@@ -24,6 +24,14 @@ def test_library_exports_every_declared_symbol(lzb):
     assert not missing, missing
 
 
+def test_scheduler_library_exports_its_header(lzb):
+    """libcudapipe.so (the C++ CUDAPipe with its C view) against include/lzb200_sched.h."""
+    assert _declared("lzb200_sched.h") == sorted(lzb.SCHED_SYMBOLS)
+    lib = lzb.sched_lib()
+    missing = [s for s in _declared("lzb200_sched.h") if not hasattr(lib, s)]
+    assert not missing, missing
+
+
 def test_no_cpu_fallback(lzb):
     """Without a CUDA device the library must refuse, not compute elsewhere."""
     import torch
@@ -34,6 +42,8 @@ def test_no_cpu_fallback(lzb):
     net = lzb.weights.synthetic_network(1, 8, 1)
     with pytest.raises(lzb.LzbError):
         lzb.Pipe(net, "fp32")
+    with pytest.raises(RuntimeError):
+        lzb.Scheduler(lzb.weights.prepare(lzb.weights.synthetic_raw_network(1, 8, 1)), "fp32")
 
 
 def test_product_does_not_touch_the_oracle():

@@ -91,3 +91,46 @@ def test_cudapipe_on_gpu_from_many_threads(tmp_path, lzb, oracle, precision, thr
     assert np.abs(got[:, :722] - pol).max() <= rel * scale
     assert np.abs(got[:, 722:] - val).max() <= rel * scale
     assert "positions %d" % (n + 1) in r.stdout     # every request reached the backend exactly once
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("precision,rel", [("fp32", 1e-5), ("fp16x2", 1e-2)])
+def test_scheduler_blocks_of_positions_from_threads(lzb, oracle, precision, rel):
+    """The C view of CUDAPipe (include/lzb200_sched.h): 8 threads hand in blocks
+    of 1 to 40 positions (batch size 16, so large blocks are cut), every
+    position compared with the CPU reference.  The positions are stone planes,
+    so the batches travel to the GPU as bit planes; one block with a value that
+    is neither 0 nor 1 takes the fp32 route and must agree too."""
+    import threading
+    W = lzb.weights
+    net = W.synthetic_network(2, 64, 2071, calibrated=True)
+    n = 8 * 61
+    x = W.synthetic_positions(n, 1071).reshape(n, -1)
+    x[5, 100] = 0.5
+    pol_ref, val_ref = oracle.cpu_pipe(net).forward(x)
+    sched = lzb.Scheduler(net, precision, gpus=(0,), batch_size=16, num_threads=32, eager=True)
+    pol = np.empty((n, 2, 361), np.float32)
+    val = np.empty((n, 361), np.float32)
+
+    def caller(t):
+        at = t * 61
+        for size in (1, 40, 7, 13):
+            pol[at:at + size], val[at:at + size] = sched.forward(x[at:at + size])
+            at += size
+
+    ts = [threading.Thread(target=caller, args=(t,)) for t in range(8)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    st = sched.stats()
+    scale = max(np.abs(pol_ref).max(), np.abs(val_ref).max())
+    assert np.abs(pol.reshape(n, -1) - pol_ref).max() <= rel * scale
+    assert np.abs(val - val_ref).max() <= rel * scale
+    assert st["positions"] == n and st["live_gpus"] == 1
+    assert 0 < st["bit_plane_batches"] < st["batches"]
+    sched.drain()
+    with pytest.raises(lzb.SchedulerHalted):
+        sched.forward(x[:2])
+    sched.resume()
+    p2, _ = sched.forward(x[:2])
+    assert np.abs(p2 - pol[:2]).max() <= rel * scale
+    sched.close()
