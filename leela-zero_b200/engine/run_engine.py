@@ -106,8 +106,12 @@ if __name__ == "__main__":
     ap.add_argument("--cpu-only", action="store_true", help="the reference's CPUPipe instead of the GPU")
     ap.add_argument("--selfchecks", type=int, default=0)
     ap.add_argument("--deterministic", type=int, default=0, metavar="BYTES")
-    ap.add_argument("--weights", default=None)
+    ap.add_argument("--weights", default=None,
+                    help="weights file to play with; if it does not exist yet, the random-init network "
+                         "of --blocks x --filters is written there first (and kept)")
     a = ap.parse_args()
+    if a.weights and not os.path.exists(a.weights):
+        write_network(a.blocks, a.filters, 2004, a.weights)
     out = run(a.blocks, a.filters, a.threads, a.batch, a.gpus, a.visits, a.moves,
               a.precision, weights=a.weights, games=a.games, batching=a.batching,
               cpu_only=a.cpu_only, selfchecks=a.selfchecks, deterministic=a.deterministic)

@@ -306,6 +306,26 @@ def calibrate_batchnorm(raw, positions):
     return out
 
 
+def layer_activation_rms(raw, positions):
+    """Root mean square of every 3x3 layer's output (after batch norm, residual
+    and ReLU) of a raw network on ``positions``, fp32 on the CPU: one value per
+    layer.  Used to check that a network calibrated on a few positions behaves
+    the same on the positions it is then evaluated on."""
+    eps = np.float32(1e-5)
+    x = np.asarray(positions, np.float32).reshape(-1, INPUT_PLANES, BOARD, BOARD)
+    res, rms = None, []
+    for l, w in enumerate(raw["conv_w"]):
+        y = conv3x3_direct(x, w) + raw["conv_b"][l][None, :, None, None]
+        z = (y - raw["bn_mean"][l][None, :, None, None]) / np.sqrt(raw["bn_var"][l] + eps)[None, :, None, None]
+        if l > 0 and l % 2 == 0:
+            z = z + res
+        x = np.maximum(z, 0).astype(np.float32)
+        if l % 2 == 0:
+            res = x
+        rms.append(float(np.sqrt(np.mean(np.square(x, dtype=np.float64)))))
+    return rms
+
+
 def synthetic_network(blocks, channels, seed, calibrated=False, calibration_positions=4):
     """Seeded random-init network, prepared for a pipe.  ``calibrated`` applies
     :func:`calibrate_batchnorm` on synthetic positions drawn from seed + 1."""

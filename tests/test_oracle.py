@@ -206,3 +206,22 @@ def test_calibrated_network_keeps_activations_bounded(oracle, W):
     cal = oracle.PortPipe(W.synthetic_network(20, 32, 18, calibrated=True)).forward(x)
     assert np.abs(cal[0]).max() < 100
     assert np.abs(lit[0]).max() > 10 * np.abs(cal[0]).max()
+
+
+def test_calibrated_network_behaves_alike_on_calibration_and_test_positions(lzb):
+    """The batch-norm statistics of the deep benchmark networks are measured on
+    4 synthetic positions (weights.calibrate_batchnorm); every accuracy figure
+    is then taken on other positions.  Per layer, the activation RMS on test
+    positions must stay within a factor of 2 of the RMS on the calibration
+    positions (it stays within 10 %), and over the 41 layers it may grow like
+    the square root of the depth (measured 3.8x), not geometrically."""
+    W = lzb.weights
+    seed = 2003
+    raw = W.synthetic_raw_network(20, 256, seed)
+    cal_x = W.synthetic_positions(4, seed + 1)
+    raw = W.calibrate_batchnorm(raw, cal_x)
+    on_cal = np.array(W.layer_activation_rms(raw, cal_x))
+    on_test = np.array(W.layer_activation_rms(raw, W.synthetic_positions(6, 1020)))
+    ratio = on_test / on_cal
+    assert ratio.max() <= 2.0 and ratio.min() >= 0.5, ratio
+    assert on_test[-1] <= 6.5 * on_test[2], on_test
