@@ -37,6 +37,14 @@ extern "C" {
  *  LZB_FP16, LZB_BF16  16-bit operands on the tensor cores (tcgen05), fp32
  *                      accumulation; each 3x3 layer is one implicit-GEMM
  *                      convolution with batch-norm/residual/ReLU in its epilogue.
+ *                      LZB_FP16 is the fast mode: on 20 and 40 block networks
+ *                      its winrate error reaches 6-7e-3 on a few per cent of
+ *                      positions (policy within 2e-3).  The bf16 modes
+ *                      (3 fewer mantissa bits) are an order of magnitude
+ *                      coarser and hold only the engine's self-check (L2 of
+ *                      policy and winrate differences <= 0.2,
+ *                      src/Network.cpp:667-690); use LZB_FP16_X2 where the
+ *                      half-precision bounds must hold for every position.
  *                      (Runs on CTA pairs; the environment variable
  *                      LZB_CONV_PAIRS=0, read at lzb_pipe_create, selects the
  *                      bit-identical single-CTA kernel for diagnostics.)
