@@ -50,7 +50,8 @@ FLOPS_GEMM_PER_POS = 2 * 36 * 25 * FILTERS * FILTERS
 # algorithmic FLOPs of one 3x3 layer per position as a direct convolution (C = K = 256)
 FLOPS_CONV_PER_POS = 2 * 9 * FILTERS * FILTERS * 361
 # DRAM traffic (read + write) of one conv_direct_kernel launch at 256 positions, from the committed ncu capture
-GEMM_DRAM_BYTES_PER_LAUNCH = {"fp16": 90.1e6}   # per mode; fp16: mean of two captured launches (66 and 113 MB)
+# per mode, mean over the tower layers of a step (ncu captures of two launches of each kind of layer)
+GEMM_DRAM_BYTES_PER_LAUNCH = {"fp16": 90.1e6, "fp16x2": 126.4e6}
 
 
 def load_package():
@@ -219,22 +220,6 @@ def calibrated_raw_network(W, blocks, filters, seed, rank, world):
     return raw
 
 
-def default_micro_batch(precision, B):
-    """Positions per pass through the tower as the library chooses them: the
-    whole batch for the direct convolution, 64 in fp32, and in the 16-bit
-    Winograd modes the first count from 64 up for which the transform kernel's
-    grid (FILTERS / 64 x positions) is whole waves of the SMs."""
-    if precision in ("fp16", "bf16", "fp16x2", "fp16x3"):
-        return B
-    n = 64
-    if precision != "fp32":
-        import torch
-        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-        groups = -(-FILTERS // 64)
-        n = next((c for c in range(64, min(2 * sms, 256) + 1) if (groups * c) % sms == 0), 64)
-    return min(n, B)
-
-
 def config2_sweep(pkg, W, torch, dev, device_index, precision):
     """Config 2: 20 blocks x 256 filters at batch 1 / 8 / 32 / 128, device-resident,
     complete evaluations, CUDA events on the context's stream around 20 steps each."""
@@ -361,6 +346,7 @@ def main():
     ctx = pipe.context(B)
     if args.micro_batch:
         ctx.set_micro_batch(args.micro_batch)
+    ctx_micro = ctx.micro_batch     # positions per pass through the tower, as the library chose
     stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
 
     # rotating input batches: host (pinned) and device copies
@@ -469,7 +455,7 @@ def main():
         e2e = whole_job_rate(B, world, ms_e2e)
         g_ms, g_n = prof["contraction"]
         winograd = args.precision not in ("fp16", "bf16", "fp16x2", "fp16x3")
-        micro = args.micro_batch or default_micro_batch(args.precision, B)
+        micro = ctx_micro
         # every contraction launch but the input layer's covers one micro-batch of one tower
         # layer; the last micro-batch of a step may be shorter, so take the mean size
         passes = -(-B // micro)

@@ -244,6 +244,8 @@ void* lzb_ctx_stream(lzb_ctx* c);
  * default.
  */
 int lzb_ctx_set_micro_batch(lzb_ctx* c, int positions);
+/* The count in force (the library's own choice unless set). */
+int lzb_ctx_micro_batch(const lzb_ctx* c);
 
 /* Kernel launches issued by this context since it was created. */
 long long lzb_ctx_launch_count(const lzb_ctx* c);

@@ -31,7 +31,7 @@ SYMBOLS = (
     "lzb_ctx_debug_conv", "lzb_ctx_profile_begin", "lzb_ctx_profile_end",
     "lzb_conv3x3_static", "lzb_ctx_debug_wait_probe", "lzb_host_alloc", "lzb_host_free",
     "lzb_pipe_push_conv_filters", "lzb_ctx_forward_packed", "lzb_ctx_forward_heads_packed",
-    "lzb_pipe_set_low_plane_blocks",
+    "lzb_pipe_set_low_plane_blocks", "lzb_ctx_micro_batch",
 )
 
 _f32p = ctypes.POINTER(ctypes.c_float)
@@ -71,6 +71,7 @@ def lib():
         L.lzb_ctx_sync.argtypes = [vp]
         L.lzb_ctx_stream.argtypes = [vp]
         L.lzb_ctx_set_micro_batch.argtypes = [vp, ctypes.c_int]
+        L.lzb_ctx_micro_batch.argtypes = [vp]
         L.lzb_ctx_launch_count.argtypes = [vp]
         L.lzb_ctx_debug_conv.argtypes = [vp, ctypes.c_int, _f32p, ctypes.c_int, _f32p, _f32p]
         L.lzb_ctx_profile_begin.argtypes = [vp]
@@ -247,6 +248,11 @@ class Context:
 
     def set_micro_batch(self, n):
         check(lib().lzb_ctx_set_micro_batch(self.h, n))
+
+    @property
+    def micro_batch(self):
+        """Positions per pass through the tower (the library's choice unless set)."""
+        return lib().lzb_ctx_micro_batch(self.h)
 
     @property
     def launches(self):

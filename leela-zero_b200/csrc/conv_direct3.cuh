@@ -34,6 +34,17 @@
 //      received ones in chunk order, applies batch-norm / residual / ReLU and
 //      stores the tile by TMA exactly like the other kernels.
 //
+// Two-plane activations (kPlanes == 3, LZB_FP16_X2): the e5m2 planes of a cell
+// row are cut into 128-byte chunks exactly as conv_direct2.cuh cuts them, and
+// there are never more of them than fp16 chunks.  Pair p < nlow runs e5m2 chunk
+// p as a second pass into the same accumulator: its window has a buffer of its
+// own (the operand area is sized for the exchange and has 26 KB to spare while
+// the MMAs run), and its nine weight tiles reuse the nine fp16 slots one by
+// one, each as soon as the fp16 MMAs of that tap have retired (one commit and
+// one "slot free" barrier per tap), so that the second pass's loads trail the
+// first pass's MMAs by one tap.  The epilogue is the two-plane one of the other
+// kernels (fp16 tile by TMA, byte planes by direct stores).
+//
 // All waits on mbarriers are bounded; a thread that gives up still arrives at
 // every cluster barrier, so its peers are never left waiting.
 #pragma once
@@ -50,6 +61,7 @@ using dc2::cluster_sync_all;
 using dc2::mbar_expect_tx_cluster;
 using dc2::tma_load_2d_pair;
 using dc2::tcgen05_mma_f16_pair;
+using dc2::tcgen05_mma_f8_pair;
 using dc2::kPairM;
 
 constexpr int kTaps = 9;
@@ -66,10 +78,12 @@ constexpr uint32_t kOperand3Bytes =
 constexpr uint32_t kD3SmemBytes =
     kOperand3Bytes + 8 * kStageOutBytes + 2 * kMaxN * 4 + kBarBytes + 1024;
 static_assert(kD3SmemBytes <= 227 * 1024, "shared memory of one CTA");
+static_assert(kOperand3Bytes >= 2 * kWinBytes + kWAreaBytes, "room for the second pass's window");
 constexpr uint32_t kTmemCols3 = 256;
 
 constexpr int kErrD3MmaFull = 401;
 constexpr int kErrD3Epilogue = 402;
+constexpr int kErrD3Producer = 403;
 
 // Arrive on the barrier at this offset in the two CTAs `first`, `first + 1` of
 // the cluster once the pair's MMAs issued so far have retired.
@@ -101,17 +115,25 @@ __device__ __forceinline__ uint32_t block_word(int row, int v) {
 // tmO : outputs [Qa][Kp], box 32 x 32, 64-byte swizzle.
 // Launched with cluster dimension 2 * kchunks and grid = tiles * 2 * kchunks;
 // requires Kp == 64 * kchunks (a tower layer: as many output groups as chunks).
-template <typename T>
+// tmXl, tmWl : byte maps over the e5m2 planes of the activations and over the
+// e5m2 weights (box 128 x kWinRows, box 128 x Kp/2); nlow : e5m2 chunks of
+// this layer (0 .. kchunks); ldr : elements of T per cell row of the residual
+// tensor; out_lo, out_hi8, out_pitch, q_rows as in conv_direct2_kernel.  All
+// ignored when kPlanes == 1 except ldr.
+template <typename T, int kPlanes>
 __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
     const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
     const __grid_constant__ CUtensorMap tmO, const T* res, const float* __restrict__ bn_mean,
-    const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int* err) {
+    const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int* err,
+    const __grid_constant__ CUtensorMap tmXl, const __grid_constant__ CUtensorMap tmWl, int nlow,
+    int ldr, unsigned char* out_lo, unsigned char* out_hi8, int out_pitch, int q_rows) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* smem = smem_raw + (base - raw);
     const uint32_t win_base = base;
     const uint32_t w_base = base + kWinBytes;
+    const uint32_t win2_base = base + kWinBytes + kWAreaBytes;   // second pass's window
     unsigned char* recv = smem;                               // the operand area after step 4:
     unsigned char* send = smem + kExchangeBytes;              // [receive area][send area]
     unsigned char* stage_out = smem + kOperand3Bytes;
@@ -125,6 +147,8 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
     const uint32_t rfull_bar = bars + 8u * 11;                         // every CTA: incoming partial sums
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_mem + 8 * 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_mem + 8 * 12 + 8);
+    auto bempty_bar = [&](int t) { return bars + 8u * (16 + t); };    // both CTAs of the pair: slot t is free
+    const uint32_t wfull2_bar = bars + 8u * 25;                        // leader's: second pass's window
 
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -139,6 +163,8 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
         mbar_init(wfull_bar, 2);
         mbar_init(tfull_bar, 1);
         mbar_init(rfull_bar, 1);
+        for (int i = 0; i < kTaps; i++) mbar_init(bempty_bar(i), 1);
+        mbar_init(wfull2_bar, 2);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -163,6 +189,8 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
     if (threadIdx.x == 0) mbar_expect_tx(rfull_bar, static_cast<uint32_t>(kchunks - 1) * kSlotBytes);
     const int half_n = Kp >> 1;                        // weight rows each CTA stages per tap
     const int m0 = tile * kPairM + static_cast<int>(h) * kTileM;
+    // this pair's second pass: e5m2 chunk p of the activation planes
+    const bool pass2 = kPlanes == 3 && static_cast<int>(p) < nlow;
 
     // ------------------------------------------------ TMA producer (warp 0 of every CTA)
     // The weights are constant, so their tiles are requested before this kernel
@@ -185,6 +213,20 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
             const uint32_t wf = map_to_cta(wfull_bar, lead);
             mbar_expect_tx_cluster(wf, kWinBytes);
             tma_load_2d_pair(win_base, &tmX, static_cast<int>(p) * kChunkK, m0 - kWinPad, wf);
+            if (pass2) {
+                const uint32_t wf2 = map_to_cta(wfull2_bar, lead);
+                mbar_expect_tx_cluster(wf2, kWinBytes);
+                tma_load_2d_pair(win2_base, &tmXl, static_cast<int>(p) * 128, m0 - kWinPad, wf2);
+                const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
+                for (int tap = 0; tap < kTaps; ++tap) {
+                    // slot `tap` is free once the first pass's MMAs of that tap have retired
+                    if (!mbar_wait(bempty_bar(tap), 0u, abort_flag, err, kErrD3Producer)) break;
+                    const uint32_t bf = map_to_cta(bfull_bar(tap), lead);
+                    mbar_expect_tx_cluster(bf, btx);
+                    tma_load_2d_pair(w_base + tap * kWStageBytes, &tmWl, static_cast<int>(p) * 128,
+                                     tap * Kp + static_cast<int>(h) * half_n, bf);
+                }
+            }
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer (pair leaders)
@@ -205,6 +247,26 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
                 for (int k = 0; k < kChunkK / 16; ++k) {
                     tcgen05_mma_f16_pair(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc,
                                          (tap > 0 || k > 0) ? 1u : 0u);
+                }
+                if (pass2) tcgen05_commit_to_pair(bempty_bar(tap), lead);
+            }
+            if (pass2 && ok) {
+                // e5m2 x e5m2 -> fp32, K = 32 per instruction: again 32 bytes of every row
+                const uint32_t idesc8 = (1u << 4) | (1u << 7) | (1u << 10) |
+                                        (static_cast<uint32_t>(Kp >> 3) << 17) |
+                                        (static_cast<uint32_t>(kPairM >> 4) << 24);
+                ok = mbar_wait(wfull2_bar, 0u, abort_flag, err, kErrD3MmaFull);
+                for (int tap = 0; tap < kTaps && ok; ++tap) {
+                    ok = mbar_wait(bfull_bar(tap), 1u, abort_flag, err, kErrD3MmaFull);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const int row0 = kWinPad + (tap / 3 - 1) * kCellsPerRow + (tap % 3 - 1);
+                    const uint64_t a_desc = umma_desc_sw128(win2_base + static_cast<uint32_t>(row0) * 128u);
+                    const uint64_t b_desc = umma_desc_sw128(w_base + tap * kWStageBytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        tcgen05_mma_f8_pair(tmem_base, a_desc + 2u * k, b_desc + 2u * k, idesc8, 1u);
+                    }
                 }
             }
             // also after a failed wait: the epilogue warps of both CTAs must not
@@ -268,8 +330,13 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
         const int q = row0 + lane;
         const bool interior = cell_is_interior(q, Q);
         const bool use_res = (res != nullptr) && interior;
-        uint4 rv[4];
-        load_residual(rv, res + static_cast<size_t>(q) * Kp + col0, use_res);
+        uint4 rv[4], re[2];
+        load_residual(rv, res + static_cast<size_t>(q) * ldr + col0, use_res);
+        if constexpr (kPlanes == 3) {
+            // e5m2 plane of the same row: Kp bytes after the Kp 16-bit channels
+            load_residual8(re, reinterpret_cast<const unsigned char*>(res + static_cast<size_t>(q) * ldr + Kp) + col0,
+                           use_res);
+        }
         uint32_t own[32];
         LZB_TMEM_LD32(own, tmem_base + tlane + static_cast<uint32_t>(col0));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -301,9 +368,29 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(acc[i]);
             unsigned char* stg_ptr = stage_out + (warp - 2) * kStageOutBytes;
-            epilogue_chunk<T>(r, rv, s_scale + col0, s_bias + col0, use_res, interior,
-                              stg_ptr + lane * 64, lane);
-            store_staged_tile(&tmO, smem_u32(stg_ptr), col0, row0, lane);
+            if constexpr (kPlanes == 3) {
+                uint32_t lo[8], h8[8];
+                epilogue_chunk_e5m2<T>(r, rv, re, s_scale + col0, s_bias + col0, use_res, interior,
+                                       stg_ptr + lane * 64, lane, lo, h8, out_hi8 != nullptr);
+                store_staged_tile(&tmO, smem_u32(stg_ptr), col0, row0, lane);
+                if (q < q_rows) {
+                    const size_t off = static_cast<size_t>(q) * out_pitch + col0;
+                    if (out_lo != nullptr) {
+                        uint4* dst = reinterpret_cast<uint4*>(out_lo + off);
+                        dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        dst[1] = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                    }
+                    if (out_hi8 != nullptr) {
+                        uint4* dst = reinterpret_cast<uint4*>(out_hi8 + off);
+                        dst[0] = make_uint4(h8[0], h8[1], h8[2], h8[3]);
+                        dst[1] = make_uint4(h8[4], h8[5], h8[6], h8[7]);
+                    }
+                }
+            } else {
+                epilogue_chunk<T>(r, rv, s_scale + col0, s_bias + col0, use_res, interior,
+                                  stg_ptr + lane * 64, lane);
+                store_staged_tile(&tmO, smem_u32(stg_ptr), col0, row0, lane);
+            }
             if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         }
     }

@@ -280,10 +280,22 @@ int launch_gemm_f32(lzb_ctx* c, const Layer& L, int P) {
     lzb_pipe* p = c->pipe;
     {
         LaunchScope scope(c, kClassContraction);
-        const dim3 grid(round_up(P, kSimtTile) / kSimtTile, p->Cp / kSimtTile, kPoints);
-        gemm_f32_kernel<<<grid, 256, 0, c->stream>>>(static_cast<const float*>(c->V),
-                                                     static_cast<const float*>(L.U),
-                                                     static_cast<float*>(c->M), c->Pa, L.cin_p, p->Cp);
+        // 128-row tiles (V and M have Pa rows, a multiple of 128; rows beyond P
+        // are scratch), 128 output channels per tile where they divide evenly;
+        // persistent CTAs, two per SM
+        const int bn = p->Cp % 128 == 0 ? 128 : 64;
+        const int row_tiles = round_up(P, kSimtBigM) / kSimtBigM;
+        const int tiles = row_tiles * (p->Cp / bn) * kPoints;
+        const int grid = tiles < 2 * p->sm_count ? tiles : 2 * p->sm_count;
+        if (bn == 128) {
+            gemm_f32_big_kernel<128><<<grid, 256, 0, c->stream>>>(
+                static_cast<const float*>(c->V), static_cast<const float*>(L.U),
+                static_cast<float*>(c->M), c->Pa, L.cin_p, p->Cp, row_tiles);
+        } else {
+            gemm_f32_big_kernel<64><<<grid, 256, 0, c->stream>>>(
+                static_cast<const float*>(c->V), static_cast<const float*>(L.U),
+                static_cast<float*>(c->M), c->Pa, L.cin_p, p->Cp, row_tiles);
+        }
     }
     LZB_CUDA(cudaGetLastError());
     return LZB_OK;
@@ -399,8 +411,8 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
         // Few tiles (small batches) and a tower layer: split the reduction of
         // each tile over the pairs of one cluster.
         const int kchunks = L.cinw / tc::kChunkK;
-        if (p->aplanes == 1 && kchunks >= 2 && kchunks <= dc3::kMaxSplit && p->Cp == kchunks * dc3::kGroupCols &&
-            npairs <= p->ksplit_max_tiles[kchunks]) {
+        if ((p->aplanes == 1 || p->aplanes == 3) && kchunks >= 2 && kchunks <= dc3::kMaxSplit &&
+            p->Cp == kchunks * dc3::kGroupCols && L.lchunks <= kchunks && npairs <= p->ksplit_max_tiles[kchunks]) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(npairs * 2 * kchunks);
             cfg.blockDim = dim3(dc::kDcThreads);
@@ -418,9 +430,20 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
             cudaError_t le;
             {
                 LaunchScope scope(c, kClassContraction);
-                le = cudaLaunchKernelEx(&cfg, dc3::conv_ksplit_kernel<T>, tm_in, L.tmW2[1], tm_out, res,
+                auto kernel = dc3::conv_ksplit_kernel<T, 1>;
+                if constexpr (std::is_same<T, __half>::value) {     // the two-plane mode is fp16 only
+                    if (p->aplanes == 3 && (L.out_lo || L.lchunks > 0)) kernel = dc3::conv_ksplit_kernel<T, 3>;
+                }
+                const CUtensorMap& in_lo = tm_in_lo ? *tm_in_lo : tm_in;
+                const CUtensorMap& w_lo = L.Wd8 ? L.tmW8[1] : L.tmW2[1];
+                unsigned char* out_lo =
+                    (L.out_lo && out) ? static_cast<unsigned char*>(out) + (size_t)p->Cp * p->elt : nullptr;
+                unsigned char* out_hi8 =
+                    (L.out_hi8 && out) ? static_cast<unsigned char*>(out) + (size_t)p->Cp * (p->elt + 1) : nullptr;
+                le = cudaLaunchKernelEx(&cfg, kernel, tm_in, L.tmW2[1], tm_out, res,
                                         (const float*)L.mean, (const float*)L.invstd, Q, p->Cp, kchunks,
-                                        c->d_err);
+                                        c->d_err, in_lo, w_lo, L.lchunks, p->row_bytes() / p->elt, out_lo,
+                                        out_hi8, p->row_bytes(), c->Qa);
             }
             LZB_CUDA(le);
             LZB_CUDA(cudaGetLastError());
@@ -589,9 +612,11 @@ int set_smem_attrs() {
             LZB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
         }
     }
-    LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__half>,
+    LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__half, 1>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc3::kD3SmemBytes));
-    LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__nv_bfloat16>,
+    LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__half, 3>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dc3::kD3SmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__nv_bfloat16, 1>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc3::kD3SmemBytes));
     return LZB_OK;
 }
@@ -612,7 +637,7 @@ int ksplit_resident_clusters(int csize) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, dc3::conv_ksplit_kernel<T>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, dc3::conv_ksplit_kernel<T, 1>, &cfg) != cudaSuccess) {
         (void)cudaGetLastError();
         return 0;
     }
@@ -992,7 +1017,7 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
     p->sm_count = prop.multiProcessorCount;
     // LZB_CONV_KSPLIT=0 keeps small batches on the sliced CTA-pair kernel
     // (cross-check and diagnostics).
-    if (p->pairs && aplanes == 1 && !(getenv("LZB_CONV_KSPLIT") != nullptr && atoi(getenv("LZB_CONV_KSPLIT")) == 0)) {
+    if (p->pairs && (aplanes == 1 || aplanes == 3) && !(getenv("LZB_CONV_KSPLIT") != nullptr && atoi(getenv("LZB_CONV_KSPLIT")) == 0)) {
         for (int k = 2; k <= dc3::kMaxSplit; k++) {
             p->ksplit_max_tiles[k] = precision == LZB_FP16 ? ksplit_resident_clusters<__half>(2 * k)
                                                             : ksplit_resident_clusters<__nv_bfloat16>(2 * k);
@@ -1113,6 +1138,20 @@ static int default_micro_batch(const lzb_pipe* p, int cap) {
         for (int cand = kDefaultMicroBatch; cand <= 2 * p->sm_count && cand <= kMaxMicroBatch; cand++) {
             if ((groups * cand) % p->sm_count == 0) { n = cand; break; }
         }
+    } else {
+        // fp32: the FFMA contraction runs tiles of 128 rows x 128 (or 64) channels,
+        // two CTAs per SM; take the count, from 64 down to 48, whose tiles fill
+        // their last wave best (61 positions at 256 channels: 864 tiles = 2.9 waves
+        // of 296, where 64 positions make 936 = 3.2)
+        const int col_tiles = p->Cp / (p->Cp % 128 == 0 ? 128 : 64);
+        const int slots = 2 * p->sm_count;
+        double best = 0.0;
+        for (int cand = kDefaultMicroBatch; cand >= 48; cand--) {
+            const int tiles = round_up(cand * kTilesPerPos, kSimtBigM) / kSimtBigM * col_tiles * kPoints;
+            const int waves = (tiles + slots - 1) / slots;
+            const double rate = static_cast<double>(cand) / waves;     // positions per wave
+            if (rate > best * 1.02) { best = rate; n = cand; }
+        }
     }
     return n < cap ? n : cap;
 }
@@ -1211,6 +1250,8 @@ void lzb_ctx_destroy(lzb_ctx* c) {
     if (c->h_err) cudaFreeHost(c->h_err);
     delete c;
 }
+
+int lzb_ctx_micro_batch(const lzb_ctx* c) { return c ? c->micro : 0; }
 
 int lzb_ctx_set_micro_batch(lzb_ctx* c, int positions) {
     if (!c) return fail(LZB_ERR_ARG, "null context");

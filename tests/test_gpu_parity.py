@@ -378,21 +378,25 @@ def test_single_cta_and_cta_pair_kernels_agree(lzb, W, monkeypatch):
     assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
 
 
+@pytest.mark.parametrize("mode", ["fp16", "fp16x2"])
 @pytest.mark.parametrize("filters,n", [(128, 5), (192, 3), (256, 1), (256, 8)])
-def test_reduction_split_kernel_agrees_with_sliced_kernel(lzb, oracle, W, monkeypatch, filters, n):
+def test_reduction_split_kernel_agrees_with_sliced_kernel(lzb, oracle, W, monkeypatch, filters, n, mode):
     """Small batches run each tile on one cluster whose CTA pairs split the
     input channels and add their partial sums through distributed shared
     memory; LZB_CONV_KSPLIT=0 keeps them on the CTA-pair kernel with sliced
     output channels.  Same operands, different order of the fp32 additions:
     the raw head planes agree to fp16 rounding, and both hold the 16-bit
-    tolerances against the oracle."""
-    net = W.synthetic_network(4, filters, 2070 + filters, calibrated=True)
+    tolerances against the oracle.  In fp16x2 the pairs of the cluster run the
+    e5m2 planes as a second pass (5 blocks: layers with the weight remainder,
+    with the activation plane only are all present in a 4-block default
+    schedule only up to the remainder kind, so one more block is added)."""
+    net = W.synthetic_network(5 if mode == "fp16x2" else 4, filters, 2070 + filters, calibrated=True)
     x = W.synthetic_positions(n, 1070 + n)
     _, _, rp, rw = _reference(oracle, net, x)
     outs = []
     for flag in ("1", "0"):
         monkeypatch.setenv("LZB_CONV_KSPLIT", flag)
-        pipe = lzb.Pipe(net, "fp16")
+        pipe = lzb.Pipe(net, mode)
         ctx = pipe.context(n)
         outs.append(ctx.forward(x))
         policy, win = ctx.forward_heads(x)
