@@ -12,6 +12,11 @@
  * driven from different host threads at the same time.  One context must not
  * be used by two threads at once.
  *
+ * Current device: every entry point that touches a GPU makes the device of its
+ * pipe (or its `device` argument) the calling thread's current CUDA device and
+ * leaves it current on return (cudaSetDevice); a host that relies on its own
+ * current device sets it again after calling in.
+ *
  * There is no CPU fallback: every entry point that computes needs a CUDA
  * device of compute capability 10.0 and fails with LZB_ERR_CUDA otherwise.
  */
