@@ -317,7 +317,7 @@ def main():
     ap.add_argument("--no-scheduler-level", action="store_true",
                     help="skip the measurement through the one-process scheduler (CUDAPipe)")
     ap.add_argument("--precision", default=PRECISION,
-                    choices=["fp16", "bf16", "fp16-winograd", "bf16-winograd", "fp32", "fp16x2", "fp16x3"])
+                    choices=["fp16", "bf16", "fp16-winograd", "bf16-winograd", "fp32", "fp16x2", "fp16x3", "bf16x3"])
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -454,7 +454,7 @@ def main():
         value = whole_job_rate(B, world, ms_dev)
         e2e = whole_job_rate(B, world, ms_e2e)
         g_ms, g_n = prof["contraction"]
-        winograd = args.precision not in ("fp16", "bf16", "fp16x2", "fp16x3")
+        winograd = args.precision not in ("fp16", "bf16", "fp16x2", "fp16x3", "bf16x3")
         micro = ctx_micro
         # every contraction launch but the input layer's covers one micro-batch of one tower
         # layer; the last micro-batch of a step may be shorter, so take the mean size

@@ -77,6 +77,9 @@ extern "C" {
  *                      (three MMAs: hi*hi + lo*hi + hi*lo): ten times closer
  *                      to fp32 than LZB_FP16 (what remains is the accumulation
  *                      inside the tensor cores).
+ *  LZB_BF16_X3         the same scheme on bf16 planes (two 8-bit mantissas per
+ *                      operand): the bf16 mode that holds the half-precision
+ *                      bounds, at the cost of LZB_FP16_X3.
  */
 #define LZB_FP32 0
 #define LZB_FP16 1
@@ -85,6 +88,7 @@ extern "C" {
 #define LZB_BF16_WINOGRAD 4
 #define LZB_FP16_X2 5
 #define LZB_FP16_X3 6
+#define LZB_BF16_X3 7
 
 #define LZB_INPUT_PLANES 18
 #define LZB_SQ 361

@@ -16,9 +16,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "liblzb200.so")
 
 FP32, FP16, BF16, FP16_WINOGRAD, BF16_WINOGRAD = 0, 1, 2, 3, 4
-FP16_X2, FP16_X3 = 5, 6
+FP16_X2, FP16_X3, BF16_X3 = 5, 6, 7
 PRECISIONS = {"fp32": FP32, "fp16": FP16, "bf16": BF16, "fp16-winograd": FP16_WINOGRAD,
-              "bf16-winograd": BF16_WINOGRAD, "fp16x2": FP16_X2, "fp16x3": FP16_X3}
+              "bf16-winograd": BF16_WINOGRAD, "fp16x2": FP16_X2, "fp16x3": FP16_X3,
+              "bf16x3": BF16_X3}
 IN_FLOATS, POL_FLOATS, VAL_FLOATS, MOVES = 18 * 361, 2 * 361, 361, 362
 
 # every symbol include/lzb200.h declares

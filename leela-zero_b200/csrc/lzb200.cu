@@ -478,10 +478,11 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
         {
             LaunchScope scope(c, kClassContraction);
             auto kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 1, true> : dc2::conv_direct2_kernel<T, 1, false>;
-            if constexpr (std::is_same<T, __half>::value) {     // the plane-splitting modes are fp16 only
-                if (p->aplanes == 2) {
-                    kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 2, true> : dc2::conv_direct2_kernel<T, 2, false>;
-                } else if (L.out_lo || L.lchunks > 0) {
+            if (p->aplanes == 2) {
+                kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 2, true> : dc2::conv_direct2_kernel<T, 2, false>;
+            }
+            if constexpr (std::is_same<T, __half>::value) {     // the e5m2 planes accompany fp16 only
+                if (p->aplanes == 3 && (L.out_lo || L.lchunks > 0)) {
                     kernel = nsplit > 1 ? dc2::conv_direct2_kernel<T, 3, true> : dc2::conv_direct2_kernel<T, 3, false>;
                 }
             }
@@ -607,7 +608,9 @@ int set_smem_attrs() {
             (const void*)dc2::conv_direct2_kernel<__half, 2, false>, (const void*)dc2::conv_direct2_kernel<__half, 2, true>,
             (const void*)dc2::conv_direct2_kernel<__half, 3, false>, (const void*)dc2::conv_direct2_kernel<__half, 3, true>,
             (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, false>,
-            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, true>};
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 1, true>,
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 2, false>,
+            (const void*)dc2::conv_direct2_kernel<__nv_bfloat16, 2, true>};
         for (const void* k : variants) {
             LZB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
         }
@@ -869,8 +872,13 @@ int install_conv(lzb_pipe* p, int layer, const float* src, int c_in, const float
         }
     }
     if (rc == LZB_OK && Wd32 != nullptr) {
-        dc::widen_weights_kernel<__half><<<512, 256>>>(Wd32, static_cast<__half*>(L.Wd), L.cin_p, p->Cp,
-                                                       wplanes, lo_mask);
+        if (p->precision == LZB_FP16) {
+            dc::widen_weights_kernel<__half><<<512, 256>>>(Wd32, static_cast<__half*>(L.Wd), L.cin_p, p->Cp,
+                                                           wplanes, lo_mask);
+        } else {
+            dc::widen_weights_kernel<__nv_bfloat16><<<512, 256>>>(
+                Wd32, static_cast<__nv_bfloat16*>(L.Wd), L.cin_p, p->Cp, wplanes, lo_mask);
+        }
         e = cudaGetLastError();
         if (e == cudaSuccess && L.lchunks > 0) {
             const int cin8 = L.lchunks * 128;
@@ -975,6 +983,12 @@ int lzb_pipe_create(lzb_pipe** out, int device, int channels, int blocks, int pr
             aplanes = precision == LZB_FP16_X3 ? 2 : 3;
             wsplit = (precision == LZB_FP16_X3);
             precision = LZB_FP16;
+            direct = true;
+            break;
+        case LZB_BF16_X3:
+            aplanes = 2;
+            wsplit = true;
+            precision = LZB_BF16;
             direct = true;
             break;
         case LZB_FP16_WINOGRAD: precision = LZB_FP16; break;

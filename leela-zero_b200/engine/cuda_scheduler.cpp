@@ -37,6 +37,7 @@ CUDAPipe::Precision precision_from_name(const char* name, bool* ok) {
         {"bf16-winograd", CUDAPipe::Precision::BF16_WINOGRAD},
         {"fp16x2", CUDAPipe::Precision::FP16_X2},
         {"fp16x3", CUDAPipe::Precision::FP16_X3},
+        {"bf16x3", CUDAPipe::Precision::BF16_X3},
     };
     for (const auto& row : table) {
         if (std::strcmp(row.name, name) == 0) {

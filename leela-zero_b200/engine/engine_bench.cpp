@@ -194,7 +194,7 @@ int main(int argc, char** argv) {
     }
     const CUDAPipe* pipe = lzb_engine::last_pipe;
     static const char* const mode_names[] = {"fp32", "fp16", "bf16", "fp16-winograd", "bf16-winograd",
-                                             "fp16x2", "fp16x3"};
+                                             "fp16x2", "fp16x3", "bf16x3"};
     const std::string pipe_name = cpu_only || !pipe ? "CPUPipe"
         : std::string("CUDAPipe ") + mode_names[static_cast<int>(pipe->precision())];
     auto game = std::make_unique<GameState>();

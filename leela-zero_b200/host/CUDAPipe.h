@@ -47,7 +47,7 @@
 class CUDAPipe : public ForwardPipe {
 public:
     enum class Precision { FP32 = 0, FP16 = 1, BF16 = 2, FP16_WINOGRAD = 3, BF16_WINOGRAD = 4,
-                           FP16_X2 = 5, FP16_X3 = 6 };
+                           FP16_X2 = 5, FP16_X3 = 6, BF16_X3 = 7 };
 
     // What runs a batch.  The production backend calls the lzb200 C ABI; tests
     // substitute their own to exercise the scheduler without a GPU.

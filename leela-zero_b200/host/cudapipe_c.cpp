@@ -48,7 +48,7 @@ const char* lzb_sched_last_error(void) { return g_error.c_str(); }
 int lzb_sched_create(lzb_sched** out, const int* gpus, int n_gpus, int batch_size, int num_threads,
                      int precision, int eager) {
     if (!out || n_gpus < 0 || (n_gpus > 0 && !gpus) || batch_size < 1 || num_threads < 1 ||
-        precision < 0 || precision > static_cast<int>(CUDAPipe::Precision::FP16_X3)) {
+        precision < 0 || precision > static_cast<int>(CUDAPipe::Precision::BF16_X3)) {
         return bad("lzb_sched_create: bad arguments");
     }
     return guarded([&] {

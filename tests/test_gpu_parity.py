@@ -218,18 +218,24 @@ def test_config3_40x256_batch256(lzb, oracle, W):
     policy, win = lzb.Pipe(net, "fp16x3").context(64).forward_heads(x[:64])
     ep, ew, l2 = _errors(oracle, policy, win, rp[:64], rw[:64])
     assert ep.max() <= 4e-4 and ew.max() <= 1e-3
+    # the same on bf16 planes: the bf16 mode that holds the half-precision bounds
+    policy, win = lzb.Pipe(net, "bf16x3").context(256).forward_heads(x)
+    ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
+    print("bf16x3: policy %.3g winrate %.3g" % (ep.max(), ew.max()))
+    assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16 and l2 <= SELFCHECK_MAX
 
 
 @pytest.mark.parametrize("blocks,filters,n", [(1, 8, 3), (3, 64, 9), (10, 128, 8), (6, 192, 33), (20, 256, 5)])
 def test_two_plane_modes(lzb, oracle, W, blocks, filters, n):
-    """fp16x2 / fp16x3 on shallow and deep networks, small and medium batches,
-    from Winograd-transformed weights and from plain filters: always inside the
-    half-precision bounds, fp16x3 ten times inside; results do not depend on
+    """fp16x2 / fp16x3 / bf16x3 on shallow and deep networks, small and medium
+    batches, from Winograd-transformed weights and from plain filters: always
+    inside the half-precision bounds, fp16x3 ten times inside; results do not depend on
     where the weights came from beyond fp32 rounding of the filter recovery."""
     net = W.synthetic_network(blocks, filters, 2090 + filters, calibrated=True)
     x = W.synthetic_positions(n, 1090 + n)
     _, _, rp, rw = _reference(oracle, net, x)
-    for mode, tp, tv in (("fp16x2", TOL_POLICY_16, TOL_VALUE_16), ("fp16x3", 2e-4, 5e-4)):
+    for mode, tp, tv in (("fp16x2", TOL_POLICY_16, TOL_VALUE_16), ("fp16x3", 2e-4, 5e-4),
+                         ("bf16x3", TOL_POLICY_16, TOL_VALUE_16)):
         ctx = lzb.Pipe(net, mode).context(n)
         policy, win = ctx.forward_heads(x)
         ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
