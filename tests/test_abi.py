@@ -32,6 +32,29 @@ def test_scheduler_library_exports_its_header(lzb):
     assert not missing, missing
 
 
+def test_scheduler_c_view_refuses_bad_calls(lzb):
+    """Argument and call-order errors of include/lzb200_sched.h come back as
+    status codes with a text, without a GPU being touched."""
+    import ctypes
+    L = lzb.sched_lib()
+    h = ctypes.c_void_p()
+    ids = (ctypes.c_int * 1)(0)
+    assert L.lzb_sched_create(ctypes.byref(h), ids, 1, 0, 8, lzb.FP16, 0) == 1      # batch size 0
+    assert b"bad arguments" in L.lzb_sched_last_error()
+    assert L.lzb_sched_create(ctypes.byref(h), ids, 1, 8, 8, 99, 0) == 1            # unknown precision
+    assert L.lzb_sched_create(ctypes.byref(h), ids, 1, 8, 8, lzb.FP16_X2, 1) == 0
+    x = (ctypes.c_float * 8)()
+    assert L.lzb_sched_forward(h, x, 1, x, x) == 1                                   # not started
+    assert b"not started" in L.lzb_sched_last_error()
+    assert L.lzb_sched_drain(h) == 1 and L.lzb_sched_resume(h) == 1
+    fp = ctypes.cast(x, ctypes.POINTER(ctypes.c_float))
+    assert L.lzb_sched_add_conv(h, None, 18, 8, fp, fp) == 1                         # null weights
+    assert L.lzb_sched_start(h, 8, None, fp) == 1
+    out = (ctypes.c_ulonglong * 8)()
+    assert L.lzb_sched_stats(h, out) == 0 and out[0] == 0
+    L.lzb_sched_destroy(h)
+
+
 def test_no_cpu_fallback(lzb):
     """Without a CUDA device the library must refuse, not compute elsewhere."""
     import torch
