@@ -115,6 +115,9 @@ __device__ __forceinline__ uint32_t block_word(int row, int v) {
 // tmO : outputs [Qa][Kp], box 32 x 32, 64-byte swizzle.
 // Launched with cluster dimension 2 * kchunks and grid = tiles * 2 * kchunks;
 // requires Kp == 64 * kchunks (a tower layer: as many output groups as chunks).
+// achunks : 64-channel chunks the activation tensor has; weight chunk c >= achunks
+// is paired with activation chunk c - achunks (a second set of weight planes
+// against the same activations, as in conv_direct2_kernel).
 // tmXl, tmWl : byte maps over the e5m2 planes of the activations and over the
 // e5m2 weights (box 128 x kWinRows, box 128 x Kp/2); nlow : e5m2 chunks of
 // this layer (0 .. kchunks); ldr : elements of T per cell row of the residual
@@ -126,7 +129,7 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
     const __grid_constant__ CUtensorMap tmO, const T* res, const float* __restrict__ bn_mean,
     const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int* err,
     const __grid_constant__ CUtensorMap tmXl, const __grid_constant__ CUtensorMap tmWl, int nlow,
-    int ldr, unsigned char* out_lo, unsigned char* out_hi8, int out_pitch, int q_rows) {
+    int ldr, unsigned char* out_lo, unsigned char* out_hi8, int out_pitch, int q_rows, int achunks) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -212,7 +215,8 @@ __global__ void __launch_bounds__(kDcThreads, 1) conv_ksplit_kernel(
         if (lane == 0) {
             const uint32_t wf = map_to_cta(wfull_bar, lead);
             mbar_expect_tx_cluster(wf, kWinBytes);
-            tma_load_2d_pair(win_base, &tmX, static_cast<int>(p) * kChunkK, m0 - kWinPad, wf);
+            const int achunk = static_cast<int>(p) < achunks ? static_cast<int>(p) : static_cast<int>(p) - achunks;
+            tma_load_2d_pair(win_base, &tmX, achunk * kChunkK, m0 - kWinPad, wf);
             if (pass2) {
                 const uint32_t wf2 = map_to_cta(wfull2_bar, lead);
                 mbar_expect_tx_cluster(wf2, kWinBytes);

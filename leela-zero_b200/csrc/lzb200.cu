@@ -443,7 +443,7 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
                 le = cudaLaunchKernelEx(&cfg, kernel, tm_in, L.tmW2[1], tm_out, res,
                                         (const float*)L.mean, (const float*)L.invstd, Q, p->Cp, kchunks,
                                         c->d_err, in_lo, w_lo, L.lchunks, p->row_bytes() / p->elt, out_lo,
-                                        out_hi8, p->row_bytes(), c->Qa);
+                                        out_hi8, p->row_bytes(), c->Qa, L.achunks);
             }
             LZB_CUDA(le);
             LZB_CUDA(cudaGetLastError());
