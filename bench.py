@@ -521,7 +521,10 @@ def main():
                 "note": "misses the winrate bound: max-abs 7.0e-3 over 256 positions (policy 1.6e-3); "
                         "95th percentile 4.2e-3"}
         if world == 1 and args.precision == PRECISION and not args.no_sweep:
-            out["config2_sweep"] = config2_sweep(pkg, W, torch, dev, local, args.precision)
+            try:
+                out["config2_sweep"] = config2_sweep(pkg, W, torch, dev, local, args.precision)
+            except Exception as e:
+                out["config2_sweep"] = {"error": repr(e)}
         if world == 1 and not args.no_cpu_baseline:
             cores = os.cpu_count() or 1
             sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -534,7 +537,13 @@ def main():
         if args.precision == PRECISION and not args.no_scheduler_level:
             ctx.close()
             pipe.close()
-            out["scheduler_level"] = scheduler_level(pkg, W, net, args.precision, range(world))
+            # an extra: its failure is reported in its own key and must not cost the line
+            try:
+                visible = torch.cuda.device_count()
+                out["scheduler_level"] = scheduler_level(pkg, W, net, args.precision,
+                                                         range(min(world, visible)))
+            except Exception as e:
+                out["scheduler_level"] = {"error": repr(e)}
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.barrier(group=host_group)
