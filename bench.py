@@ -280,14 +280,19 @@ def scheduler_level(pkg, W, net, precision, gpus, seconds=2.0, block=64, callers
         except Exception as e:   # reported, never swallowed
             failures.append(repr(e))
 
-    ts = [threading.Thread(target=caller, args=(t,)) for t in range(callers)]
+    ts = [threading.Thread(target=caller, args=(t,), daemon=True) for t in range(callers)]
     [t.start() for t in ts]
     time.sleep(0.5)
     s0, c0, t0 = sched.stats(), sum(done), time.perf_counter()
     time.sleep(seconds)
     s1, c1, t1 = sched.stats(), sum(done), time.perf_counter()
     stop.set()
-    [t.join() for t in ts]
+    deadline = time.perf_counter() + 30.0
+    for t in ts:
+        t.join(max(0.0, deadline - time.perf_counter()))
+    if any(t.is_alive() for t in ts):
+        # leave the scheduler alone (closing it would wait for the same threads) and say so
+        raise RuntimeError("scheduler_level: callers still blocked 30 s after the measurement")
     sched.close()
     if failures:
         raise RuntimeError("scheduler_level: " + failures[0])
