@@ -509,7 +509,7 @@ def main():
             "kernel_ms_per_step": {k: v[0] / prof_steps for k, v in prof.items()},
         }
         out["accuracy"] = ("policy <= 2e-3 and winrate <= 5e-3 max-abs against the reference CPUPipe on every "
-                           "position (tests/test_gpu_parity.py::test_config3_40x256_batch256)"
+                           "position of this network (tests/test_gpu_parity.py::test_config3_40x256_batch256)"
                            if args.precision == PRECISION else "see tests/test_gpu_parity.py for this mode")
         if world == 1 and args.precision == PRECISION and not args.no_fast_mode:
             # The same workload in plain fp16, device-resident: faster, but its winrate

@@ -70,9 +70,13 @@ extern "C" {
  *                      deeper than 24 blocks carries the low plane, and the
  *                      first 4 blocks also correct the rounding of their
  *                      weights with a third pair of e5m2 planes
- *                      (lzb_pipe_set_low_plane_blocks); holds the
- *                      half-precision bounds (policy 2e-3, winrate 5e-3) for
- *                      every position at 40 blocks.
+ *                      (lzb_pipe_set_low_plane_blocks).  With these counts the
+ *                      half-precision bounds (policy 2e-3, winrate 5e-3)
+ *                      hold for every position of the 40-block benchmark
+ *                      network with a factor of two to spare; a network with
+ *                      sharper outputs may need more blocks (30 and 8 held
+ *                      them on the hardest random network tried), which is
+ *                      what the counts are adjustable for.
  *  LZB_FP16_X3         activations and weights both carried as two fp16 planes
  *                      (three MMAs: hi*hi + lo*hi + hi*lo): ten times closer
  *                      to fp32 than LZB_FP16 (what remains is the accumulation

@@ -225,6 +225,29 @@ def test_config3_40x256_batch256(lzb, oracle, W):
     assert ep.max() <= TOL_POLICY_16 and ew.max() <= TOL_VALUE_16 and l2 <= SELFCHECK_MAX
 
 
+def test_low_plane_schedule_is_a_knob(lzb, oracle, W):
+    """How many blocks carry the correction planes is adjustable
+    (lzb_pipe_set_low_plane_blocks).  A random 40 x 256 network with sharper
+    outputs than the benchmark network (weight seed 2203: plain fp16 errs by
+    1e-2 on it, the default schedule by 5.1e-3 on one of these positions): with
+    30 activation blocks and 8 weight blocks the half-precision bounds hold on
+    every position, and more planes never make it worse than fewer."""
+    net = W.synthetic_network(40, 256, 2203, calibrated=True)
+    x = W.synthetic_positions(256, 1040)
+    _, _, rp, rw = _reference(oracle, net, x)
+    worst = {}
+    for sched in ((20, 4), (30, 8), (-1, -1)):
+        ctx = lzb.Pipe(net, "fp16x2", low_plane_blocks=sched[0], weight_blocks=sched[1]).context(256)
+        policy, win = ctx.forward_heads(x)
+        ep, ew, l2 = _errors(oracle, policy, win, rp, rw)
+        worst[sched] = (ep.max(), ew.max())
+        assert l2 <= SELFCHECK_MAX
+        ctx.close()
+    assert worst[(30, 8)][0] <= TOL_POLICY_16 and worst[(30, 8)][1] <= TOL_VALUE_16
+    assert worst[(-1, -1)][0] <= 0.5 * TOL_POLICY_16 and worst[(-1, -1)][1] <= 0.5 * TOL_VALUE_16
+    assert worst[(30, 8)][1] <= worst[(20, 4)][1] and worst[(-1, -1)][1] <= worst[(30, 8)][1]
+
+
 @pytest.mark.parametrize("blocks,filters,n", [(1, 8, 3), (3, 64, 9), (10, 128, 8), (6, 192, 33), (20, 256, 5)])
 def test_two_plane_modes(lzb, oracle, W, blocks, filters, n):
     """fp16x2 / fp16x3 / bf16x3 on shallow and deep networks, small and medium
