@@ -110,6 +110,75 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
         : "memory");
 }
 
+// ---- per-tile dependencies between consecutive layers (whole-tile launches) ----
+// A tile of one layer reads, through its window, only tiles i-1, i, i+1 of the
+// layer before.  When the host passes flag arrays, a launch does not wait for
+// the whole previous launch (griddepcontrol.wait): its producers wait for the
+// flags of those three tiles instead, and its epilogue warps raise their own
+// tile's flag once their stores have completed.  A dependent launch starts only
+// after every CTA of its predecessor has started (both call
+// griddepcontrol.launch_dependents first thing), so a flag that is waited for
+// always has a running or finished writer.  Per tile there are two words: a
+// counter of arrivals, 16 per evaluation of the tile (8 epilogue warps in each
+// CTA of the pair; its value is always a multiple of 16 between evaluations,
+// whatever batch sizes came before), and the number of the tower run that
+// completed the tile last, stored by the sixteenth arrival.  Neither is reset.
+constexpr uint32_t kFlagArrivals = 16;
+constexpr unsigned long long kFlagWaitLimitNs = 250000000ull;   // a layer takes about 0.1 ms
+constexpr int kErrD2Flags = 305;
+constexpr int kMaxOrder = 16;          // tiles per CTA pair the visiting order is kept for
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t atom_acq_rel_gpu_add(uint32_t* p, uint32_t v) {
+    uint32_t old;
+    asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded like every other wait of this library.
+__device__ __noinline__ bool flag_wait(const uint32_t* flag, uint32_t target, volatile int* abort_flag,
+                                       int* err) {
+    if (static_cast<int32_t>(ld_acquire_gpu(flag) - target) >= 0) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    const long long c0 = clock64();
+    for (uint32_t spin = 1;; ++spin) {
+        if (static_cast<int32_t>(ld_acquire_gpu(flag) - target) >= 0) return true;
+        __nanosleep(64);
+        if ((spin & 31u) == 0u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > kFlagWaitLimitNs &&
+                static_cast<unsigned long long>(clock64() - c0) > kFlagWaitLimitNs) {
+                *abort_flag = 1;
+                atomicCAS(err, 0, kErrD2Flags);
+                return false;
+            }
+        }
+    }
+}
+// The k-th tile a pair visits in its range [begin, begin + n): from the middle
+// outwards, the two ends last.  The first tile of a layer then depends on tiles
+// this pair finished early in the layer before, and the end tiles, which depend
+// on the neighbours' end tiles, come when those are long done.
+__device__ __forceinline__ int middle_out(int k, int n) {
+    const int m = n / 2;
+    // distances 1, 1, 2, 2, ... alternate left and right of m until one side runs out
+    const int left = m, right = n - 1 - m;           // tiles on either side of m
+    const int paired = left < right ? left : right;  // distances with both sides present
+    if (k == 0) return m;
+    if (k <= 2 * paired) {
+        const int d = (k + 1) / 2;
+        return (k & 1) ? m - d : m + d;
+    }
+    const int d = k - paired;                        // beyond: only the longer side is left
+    return left > right ? m - d : m + d;
+}
+
 // tmX : activations [Qa][Cin], box 64 x kWinRows.
 // tmW : weights [9*Kp][Cin], box 64 x Kp/(2*nsplit) (one tap's rows of one CTA's
 //       half slice; a stage of the ring takes up to three such boxes when sliced).
@@ -135,6 +204,12 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
 // exist.  tmXl, tmWl, out_lo, out_hi8 are ignored for the other kPlanes.
 // ldr : elements of T per cell row of the residual tensor (its rows may be
 // wider than Kp when the tensor also holds a low plane).
+// flags_in, flags_out, counts_out, flag_target : per-tile dependencies (above);
+// whole-tile launches only.  flags_out non-null: tiles are visited middle-out,
+// arrivals are counted in counts_out and the tile's flag is set to flag_target
+// (the number of this tower run) by the last one; flags_in non-null: the flags
+// of the previous layer's tiles are waited for instead of the previous launch
+// as a whole.
 //
 // The kernel is launched with programmatic stream serialization: it lets its
 // successor start at once (griddepcontrol.launch_dependents) and itself waits
@@ -148,7 +223,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     const float* __restrict__ bn_invstd, int Q, int Kp, int kchunks, int npairs, int nsplit,
     int* err, int achunks, const __grid_constant__ CUtensorMap tmXl,
     const __grid_constant__ CUtensorMap tmWl, int ldr, unsigned char* out_lo, int out_pitch,
-    int q_rows, int fchunks, unsigned char* out_hi8) {
+    int q_rows, int fchunks, unsigned char* out_hi8, const uint32_t* flags_in, uint32_t* flags_out,
+    uint32_t* counts_out, uint32_t flag_target) {
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -226,7 +302,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
     // stream: nobody touches them before the previous kernel has finished.
     // (Starting the constant weight tiles ahead of this wait was tried and made
     // no measurable difference.)
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const bool tile_flags = !kSliced && flags_in != nullptr;    // wait per tile, not per launch
+    if (!tile_flags) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // visiting order of this pair's tiles (whole-tile launches that raise flags)
+    const bool reorder = !kSliced && flags_out != nullptr && unit_end - unit_begin <= kMaxOrder;
+    auto tile_of = [&](int unit) {
+        return reorder ? unit_begin + middle_out(unit - unit_begin, unit_end - unit_begin) : unit / nsplit;
+    };
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer (both CTAs)
@@ -236,9 +318,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             bool ok = true;
             const uint32_t btx = static_cast<uint32_t>(half_n) * 128u;
             for (int unit = unit_begin; unit < unit_end && ok; ++unit) {
-                const int pair = unit / nsplit, slice = unit - pair * nsplit;
+                const int pair = tile_of(unit), slice = kSliced ? unit - pair * nsplit : 0;
                 const int m0 = pair * kPairM + static_cast<int>(rank) * kTileM;
                 const int wrow0 = slice * n_slice + static_cast<int>(rank) * half_n;
+                if (tile_flags) {
+                    // the window of this tile reaches into the tiles on either side
+                    for (int t = pair - 1; t <= pair + 1 && ok; ++t) {
+                        if (t >= 0 && t < npairs) ok = flag_wait(flags_in + t, flag_target, abort_flag, err);
+                    }
+                    if (!ok) break;
+                    // what those tiles' epilogues stored is read below by TMA (async proxy)
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                }
                 for (int c = 0; c < kchunks && ok; ++c) {
                     ok = mbar_wait(wempty_bar(wb), wphase ^ 1u, abort_flag, err, kErrD2Producer);
                     if (!ok) break;
@@ -392,7 +483,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
         unsigned char* stg_row = stg_ptr + lane * 64;
         int local = 0;
         for (int unit = unit_begin; unit < unit_end; ++unit, ++local) {
-            const int pair = unit / nsplit, slice = unit - pair * nsplit;
+            const int pair = tile_of(unit), slice = kSliced ? unit - pair * nsplit : 0;
             const int col0 = slice * n_slice + wcol;   // first output channel of this warp
             const int acc = local & 1;
             const uint32_t accphase = (local >> 1) & 1u;
@@ -480,6 +571,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDcThreads, 1) conv_
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+            if (!kSliced && flags_out != nullptr) {
+                // this warp's part of the tile is in memory: its TMA stores have
+                // completed, its lanes' direct stores are fenced; then count it
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                    // the read-modify-write chain carries every earlier arrival's writes
+                    const uint32_t before = atom_acq_rel_gpu_add(counts_out + pair, 1u);
+                    if ((before & (kFlagArrivals - 1u)) == kFlagArrivals - 1u) {
+                        st_release_gpu(flags_out + pair, flag_target);
+                    }
+                }
+            }
         }
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }

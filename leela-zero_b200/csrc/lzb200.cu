@@ -190,6 +190,12 @@ struct lzb_ctx {
     float *d_in = nullptr, *d_pol = nullptr, *d_val = nullptr;
     float *d_policy = nullptr, *d_winrate = nullptr;
     unsigned int* d_packed = nullptr;   // bit-packed input planes [max_batch][18][12]
+    // per-tile completion words of the direct path, [2][layers][tile_cap] (the run
+    // that completed a tile last, then the arrival counters), and the number of
+    // tower runs so far (see conv_direct2.cuh); null: not used
+    uint32_t* tile_flags = nullptr;
+    int tile_cap = 0;
+    uint32_t tower_runs = 0;
     int* d_err = nullptr;
     int* h_err = nullptr;  // pinned
     CUtensorMap tmV_first, tmV;
@@ -402,7 +408,9 @@ int run_tower(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, float* va
 template <typename T>
 int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm_in,
                        const CUtensorMap& tm_out, const T* res, const CUtensorMap* tm_in_lo = nullptr,
-                       void* out = nullptr) {
+                       void* out = nullptr, const uint32_t* flags_in = nullptr,
+                       uint32_t* flags_out = nullptr, uint32_t* counts_out = nullptr,
+                       uint32_t flag_target = 0) {
     lzb_pipe* p = c->pipe;
     const int Q = static_cast<int>(dc::cells_for(nb));
     if (p->pairs) {
@@ -497,7 +505,9 @@ int launch_conv_direct(lzb_ctx* c, const Layer& L, int nb, const CUtensorMap& tm
             le = cudaLaunchKernelEx(&cfg, kernel, tm_in, L.tmW2[nsplit], tm_out, res,
                                     (const float*)L.mean, (const float*)L.invstd, Q, p->Cp,
                                     kchunks + L.lchunks, npairs, nsplit, c->d_err, L.achunks, in_lo, w_lo,
-                                    ldr, out_lo, p->row_bytes(), c->Qa, kchunks, out_hi8);
+                                    ldr, out_lo, p->row_bytes(), c->Qa, kchunks, out_hi8,
+                                    nsplit == 1 ? flags_in : nullptr, nsplit == 1 ? flags_out : nullptr,
+                                    counts_out, flag_target);
         }
         LZB_CUDA(le);
         LZB_CUDA(cudaGetLastError());
@@ -529,16 +539,29 @@ int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, fl
             in_dev, static_cast<T*>(c->IN), nb);
     }
     LZB_CUDA(cudaGetLastError());
-    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, c->tmXo, nullptr, nullptr, c->X))) {
+    // Per-tile dependencies between the layers (conv_direct2.cuh) where every
+    // layer of this batch runs whole tiles on CTA pairs: more tiles than half the
+    // pairs, so that neither the channel slices nor the reduction-split kernel apply.
+    const int npairs = (static_cast<int>(dc::cells_for(nb)) + dc2::kPairM - 1) / dc2::kPairM;
+    const bool flags = c->tile_flags != nullptr && p->pairs && npairs <= c->tile_cap &&
+                       2 * npairs > p->sm_count / 2;
+    const uint32_t target = flags ? ++c->tower_runs : 0u;     // the number of this run
+    const size_t words = (size_t)(1 + 2 * p->blocks) * c->tile_cap;
+    auto layer_flags = [&](int layer) { return flags ? c->tile_flags + (size_t)layer * c->tile_cap : nullptr; };
+    auto layer_counts = [&](int layer) { return flags ? c->tile_flags + words + (size_t)layer * c->tile_cap : nullptr; };
+    if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, c->tmXo, nullptr, nullptr, c->X, nullptr,
+                                    layer_flags(0), layer_counts(0), target))) {
         return rc;
     }
     for (int b = 0; b < p->blocks; b++) {
         if ((rc = launch_conv_direct<T>(c, p->layers[1 + 2 * b], nb, c->tmX, c->tmHo, nullptr, &c->tmXl,
-                                        c->H))) {
+                                        c->H, layer_flags(2 * b), layer_flags(1 + 2 * b),
+                                        layer_counts(1 + 2 * b), target))) {
             return rc;
         }
         if ((rc = launch_conv_direct<T>(c, p->layers[2 + 2 * b], nb, c->tmH, c->tmXo, X, &c->tmHl,
-                                        c->X))) {
+                                        c->X, layer_flags(1 + 2 * b), layer_flags(2 + 2 * b),
+                                        layer_counts(2 + 2 * b), target))) {
             return rc;
         }
     }
@@ -1193,6 +1216,13 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
         alloc(&c->IN, (size_t)c->Qa * 64 * p->elt);
         alloc(&c->X, (size_t)c->Qa * p->row_bytes());
         alloc(&c->H, (size_t)c->Qa * p->row_bytes());
+        // LZB_TILE_FLAGS=1: layers of large batches depend on each other tile by
+        // tile instead of launch by launch (conv_direct2.cuh)
+        if (p->pairs && getenv("LZB_TILE_FLAGS") != nullptr && atoi(getenv("LZB_TILE_FLAGS")) == 1) {
+            c->tile_cap = (c->Qa + dc2::kPairM - 1) / dc2::kPairM;
+            // two words per layer and tile: the run that completed it last, and the arrival counter
+            alloc((void**)&c->tile_flags, (size_t)2 * (1 + 2 * p->blocks) * c->tile_cap * sizeof(uint32_t));
+        }
     } else {
         c->micro = default_micro_batch(p, c->micro_cap);
         c->Pa = round_up(c->micro_cap * kTilesPerPos, 128);
@@ -1259,7 +1289,7 @@ void lzb_ctx_destroy(lzb_ctx* c) {
         cudaStreamSynchronize(c->stream);
         cudaStreamDestroy(c->stream);
     }
-    void* ptrs[] = {c->V, c->M, c->X, c->IN, c->H, c->d_in, c->d_pol, c->d_val, c->d_policy, c->d_winrate, c->d_packed, c->d_err};
+    void* ptrs[] = {c->V, c->M, c->X, c->IN, c->H, c->d_in, c->d_pol, c->d_val, c->d_policy, c->d_winrate, c->d_packed, c->d_err, c->tile_flags};
     for (void* q : ptrs) cudaFree(q);
     if (c->h_err) cudaFreeHost(c->h_err);
     delete c;
@@ -1303,6 +1333,12 @@ int lzb_ctx_sync(lzb_ctx* c) {
         const int code = *c->h_err;
         *c->h_err = 0;
         cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
+        if (c->tile_flags != nullptr) {
+            // an abandoned run may have left a tile's arrivals short of sixteen
+            cudaMemsetAsync(c->tile_flags, 0,
+                            (size_t)2 * (1 + 2 * c->pipe->blocks) * c->tile_cap * sizeof(uint32_t), c->stream);
+            c->tower_runs = 0;
+        }
         return fail(LZB_ERR_DEVICE_WAIT,
                     "a kernel gave up a bounded wait (code " + std::to_string(code) + ")");
     }

@@ -440,6 +440,30 @@ def test_reduction_split_kernel_agrees_with_sliced_kernel(lzb, oracle, W, monkey
     assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-2 * scale
 
 
+@pytest.mark.parametrize("mode", ["fp16", "fp16x2"])
+def test_per_tile_dependencies_give_the_same_bits(lzb, W, monkeypatch, mode):
+    """LZB_TILE_FLAGS=1 (read when a context is created): the layers of a large
+    batch wait for each other tile by tile (flags raised by the epilogues)
+    instead of launch by launch, and a CTA pair visits its tiles middle-out.
+    Same arithmetic in the same order per tile, so the outputs must agree bit
+    for bit with the default path, whatever batch sizes follow one another (the
+    arrival counters are never reset) and on repeated runs."""
+    net = W.synthetic_network(12, 256, 2095, calibrated=True)
+    x = W.synthetic_positions(256, 1095)
+    pipe = lzb.Pipe(net, mode)
+    monkeypatch.setenv("LZB_TILE_FLAGS", "0")
+    plain = pipe.context(256)
+    monkeypatch.setenv("LZB_TILE_FLAGS", "1")
+    tiled = pipe.context(256)
+    for n in (256, 64, 200, 256, 24, 131, 256):      # 24 positions: below the range it applies to
+        for _ in range(3):
+            a, b = plain.forward(x[:n]), tiled.forward(x[:n])
+            assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]), n
+    plain.close()
+    tiled.close()
+    pipe.close()
+
+
 def test_untransformed_filters_and_packed_positions(lzb, oracle, W):
     """The two data formats either side of the path: filters as they stand in a
     weights file (transformed on the GPU, or used directly by the convolution
