@@ -76,7 +76,12 @@ extern "C" {
  *                      network with a factor of two to spare; a network with
  *                      sharper outputs may need more blocks (30 and 8 held
  *                      them on the hardest random network tried), which is
- *                      what the counts are adjustable for.
+ *                      what the counts are adjustable for.  (For batches of
+ *                      more than 23 positions the layers of this mode wait for
+ *                      each other tile by tile rather than launch by launch;
+ *                      the environment variable LZB_TILE_FLAGS=0 / 1, read at
+ *                      lzb_ctx_create, switches that off / on for any of the
+ *                      direct-convolution modes; results are bit-identical.)
  *  LZB_FP16_X3         activations and weights both carried as two fp16 planes
  *                      (three MMAs: hi*hi + lo*hi + hi*lo): ten times closer
  *                      to fp32 than LZB_FP16 (what remains is the accumulation

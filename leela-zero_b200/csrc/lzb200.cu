@@ -18,6 +18,8 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
+#include <chrono>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -173,6 +175,9 @@ struct lzb_pipe {
     // count 2..4; 0 = not used.
     int ksplit_max_tiles[5] = {0, 0, 0, 0, 0};
     std::vector<Layer> layers;
+    // contexts on this pipe (their streams are asked whether they are busy)
+    std::mutex ctx_mutex;
+    std::vector<lzb_ctx*> contexts;
     float* head_w = nullptr;   // [3][Cp] fp32
     bool head_convs = false;
     bool finalized = false;
@@ -196,6 +201,8 @@ struct lzb_ctx {
     uint32_t* tile_flags = nullptr;
     int tile_cap = 0;
     uint32_t tower_runs = 0;
+    bool tile_flags_always = false;     // asked for by LZB_TILE_FLAGS=1: also while other contexts are busy
+    std::atomic<long long> last_tower_ns{0};   // when this context last enqueued a tower (steady clock)
     int* d_err = nullptr;
     int* h_err = nullptr;  // pinned
     CUtensorMap tmV_first, tmV;
@@ -543,8 +550,28 @@ int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, fl
     // layer of this batch runs whole tiles on CTA pairs: more tiles than half the
     // pairs, so that neither the channel slices nor the reduction-split kernel apply.
     const int npairs = (static_cast<int>(dc::cells_for(nb)) + dc2::kPairM - 1) / dc2::kPairM;
-    const bool flags = c->tile_flags != nullptr && p->pairs && npairs <= c->tile_cap &&
-                       2 * npairs > p->sm_count / 2;
+    bool flags = c->tile_flags != nullptr && p->pairs && npairs <= c->tile_cap &&
+                 2 * npairs > p->sm_count / 2;
+    const long long now_ns = std::chrono::duration_cast<std::chrono::nanoseconds>(
+                                 std::chrono::steady_clock::now().time_since_epoch()).count();
+    if (flags && !c->tile_flags_always) {
+        // A launch that waits tile by tile holds its SMs while it waits.  Alone on
+        // the GPU that hides the turnover between layers (-4 % per step); beside
+        // another context's tower, whose launches would have filled those gaps
+        // anyway, it costs 4 %.  So: only while no other context of this pipe is at
+        // work, i.e. none has work in flight or has enqueued a tower in the last 100 ms.
+        std::lock_guard<std::mutex> lk(p->ctx_mutex);
+        for (lzb_ctx* other : p->contexts) {
+            if (other == c || other->stream == nullptr) continue;
+            if (now_ns - other->last_tower_ns.load(std::memory_order_relaxed) < 100000000ll ||
+                cudaStreamQuery(other->stream) == cudaErrorNotReady) {
+                flags = false;
+                break;
+            }
+        }
+        (void)cudaGetLastError();       // "not ready" is an answer, not an error
+    }
+    c->last_tower_ns.store(now_ns, std::memory_order_relaxed);
     const uint32_t target = flags ? ++c->tower_runs : 0u;     // the number of this run
     const size_t words = (size_t)(1 + 2 * p->blocks) * c->tile_cap;
     auto layer_flags = [&](int layer) { return flags ? c->tile_flags + (size_t)layer * c->tile_cap : nullptr; };
@@ -1216,9 +1243,15 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
         alloc(&c->IN, (size_t)c->Qa * 64 * p->elt);
         alloc(&c->X, (size_t)c->Qa * p->row_bytes());
         alloc(&c->H, (size_t)c->Qa * p->row_bytes());
-        // LZB_TILE_FLAGS=1: layers of large batches depend on each other tile by
-        // tile instead of launch by launch (conv_direct2.cuh)
-        if (p->pairs && getenv("LZB_TILE_FLAGS") != nullptr && atoi(getenv("LZB_TILE_FLAGS")) == 1) {
+        // Layers of large batches depend on each other tile by tile instead of
+        // launch by launch (conv_direct2.cuh).  Measured gain: 3-4 % per step with
+        // the e5m2 planes (LZB_FP16_X2), none without them, so that mode has it by
+        // default, used while the context is alone on the GPU (run_tower_direct);
+        // LZB_TILE_FLAGS=0 / 1, read here, switches it off / always on for any mode.
+        const char* tf = getenv("LZB_TILE_FLAGS");
+        const bool tile_flags = tf != nullptr ? atoi(tf) == 1 : p->aplanes == 3;
+        c->tile_flags_always = tf != nullptr && atoi(tf) == 1;
+        if (p->pairs && tile_flags) {
             c->tile_cap = (c->Qa + dc2::kPairM - 1) / dc2::kPairM;
             // two words per layer and tile: the run that completed it last, and the arrival counter
             alloc((void**)&c->tile_flags, (size_t)2 * (1 + 2 * p->blocks) * c->tile_cap * sizeof(uint32_t));
@@ -1247,6 +1280,10 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
         return code;
     }
     *c->h_err = 0;
+    {
+        std::lock_guard<std::mutex> lk(p->ctx_mutex);
+        p->contexts.push_back(c);
+    }
     if (p->direct) {
         int rc = make_map_2d(&c->tmIN, p->precision, c->IN, (uint64_t)c->Qa, 64, dc::kWinRows);
         // 16-bit channels of a cell row (hi [+ 16-bit lo] plane) and the row pitch
@@ -1285,6 +1322,16 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
 void lzb_ctx_destroy(lzb_ctx* c) {
     if (!c) return;
     cudaSetDevice(c->pipe->device);
+    {
+        std::lock_guard<std::mutex> lk(c->pipe->ctx_mutex);
+        auto& v = c->pipe->contexts;
+        for (size_t i = 0; i < v.size(); i++) {
+            if (v[i] == c) {
+                v.erase(v.begin() + i);
+                break;
+            }
+        }
+    }
     if (c->stream) {
         cudaStreamSynchronize(c->stream);
         cudaStreamDestroy(c->stream);

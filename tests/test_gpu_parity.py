@@ -442,9 +442,10 @@ def test_reduction_split_kernel_agrees_with_sliced_kernel(lzb, oracle, W, monkey
 
 @pytest.mark.parametrize("mode", ["fp16", "fp16x2"])
 def test_per_tile_dependencies_give_the_same_bits(lzb, W, monkeypatch, mode):
-    """LZB_TILE_FLAGS=1 (read when a context is created): the layers of a large
-    batch wait for each other tile by tile (flags raised by the epilogues)
-    instead of launch by launch, and a CTA pair visits its tiles middle-out.
+    """LZB_TILE_FLAGS=1 (read when a context is created; the default in fp16x2):
+    the layers of a large batch wait for each other tile by tile (flags raised
+    by the epilogues) instead of launch by launch, and a CTA pair visits its
+    tiles middle-out.
     Same arithmetic in the same order per tile, so the outputs must agree bit
     for bit with the default path, whatever batch sizes follow one another (the
     arrival counters are never reset) and on repeated runs."""
