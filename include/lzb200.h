@@ -81,7 +81,9 @@ extern "C" {
  *                      each other tile by tile rather than launch by launch;
  *                      the environment variable LZB_TILE_FLAGS=0 / 1, read at
  *                      lzb_ctx_create, switches that off / on for any of the
- *                      direct-convolution modes; results are bit-identical.)
+ *                      direct-convolution modes; LZB_TOWER_KERNEL=1 on top
+ *                      of it runs all layers of such a batch in one
+ *                      cooperative launch; results are bit-identical.)
  *  LZB_FP16_X3         activations and weights both carried as two fp16 planes
  *                      (three MMAs: hi*hi + lo*hi + hi*lo): ten times closer
  *                      to fp32 than LZB_FP16 (what remains is the accumulation

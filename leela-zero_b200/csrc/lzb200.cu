@@ -29,6 +29,7 @@
 #include "conv_direct.cuh"
 #include "conv_direct2.cuh"
 #include "conv_direct3.cuh"
+#include "conv_tower.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tcgen05.cuh"
 #include "head_kernels.cuh"
@@ -175,6 +176,10 @@ struct lzb_pipe {
     // count 2..4; 0 = not used.
     int ksplit_max_tiles[5] = {0, 0, 0, 0, 0};
     std::vector<Layer> layers;
+    // per-layer records of the one-launch tower kernel (conv_tower.cuh), on the
+    // device; null where that kernel does not apply
+    lzb::dct::TowerLayer* tower_table = nullptr;
+    bool tower_refused = false;         // a cooperative launch of it failed once: not tried again
     // contexts on this pipe (their streams are asked whether they are busy)
     std::mutex ctx_mutex;
     std::vector<lzb_ctx*> contexts;
@@ -202,6 +207,7 @@ struct lzb_ctx {
     int tile_cap = 0;
     uint32_t tower_runs = 0;
     bool tile_flags_always = false;     // asked for by LZB_TILE_FLAGS=1: also while other contexts are busy
+    bool tower_kernel = false;          // LZB_TOWER_KERNEL=1: all layers of a large batch in one launch
     std::atomic<long long> last_tower_ns{0};   // when this context last enqueued a tower (steady clock)
     int* d_err = nullptr;
     int* h_err = nullptr;  // pinned
@@ -217,6 +223,7 @@ struct lzb_ctx {
     bool profiling = false;
     std::vector<cudaEvent_t> prof_events;   // 2 per launch
     std::vector<int> prof_class;
+    std::vector<int> prof_layers;           // layers a launch covers (1, or the whole tower)
 };
 
 namespace {
@@ -271,7 +278,7 @@ enum KernelClass { kClassContraction = 0, kClassTransform = 1, kClassInput = 2, 
 // Counts a launch and, while profiling, brackets it with two events.
 struct LaunchScope {
     lzb_ctx* c;
-    LaunchScope(lzb_ctx* ctx, int cls) : c(ctx) {
+    LaunchScope(lzb_ctx* ctx, int cls, int layers = 1) : c(ctx) {
         c->launches++;
         if (c->profiling) {
             cudaEvent_t a, b;
@@ -280,6 +287,7 @@ struct LaunchScope {
             c->prof_events.push_back(a);
             c->prof_events.push_back(b);
             c->prof_class.push_back(cls);
+            c->prof_layers.push_back(layers);
             cudaEventRecord(a, c->stream);
         }
     }
@@ -576,6 +584,54 @@ int run_tower_direct(lzb_ctx* c, const float* in_dev, int nb, float* pol_dev, fl
     const size_t words = (size_t)(1 + 2 * p->blocks) * c->tile_cap;
     auto layer_flags = [&](int layer) { return flags ? c->tile_flags + (size_t)layer * c->tile_cap : nullptr; };
     auto layer_counts = [&](int layer) { return flags ? c->tile_flags + words + (size_t)layer * c->tile_cap : nullptr; };
+    if (flags && c->tower_kernel && p->tower_table != nullptr && !p->tower_refused) {
+        // every layer in one cooperative launch (conv_tower.cuh)
+        const int max_clusters = p->sm_count / 2;
+        const int rounds = (npairs + max_clusters - 1) / max_clusters;
+        const int clusters = (npairs + rounds - 1) / rounds;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * clusters);
+        cfg.blockDim = dim3(dc::kDcThreads);
+        cfg.dynamicSmemBytes = dct::kTowerSmemBytes;
+        cfg.stream = c->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        auto kernel = dct::conv_tower_kernel<T, 1>;
+        if constexpr (std::is_same<T, __half>::value) {
+            if (p->aplanes == 3) kernel = dct::conv_tower_kernel<T, 3>;
+        }
+        const int n_layers = static_cast<int>(p->layers.size());
+        cudaError_t le;
+        {
+            LaunchScope scope(c, kClassContraction, n_layers);
+            le = cudaLaunchKernelEx(&cfg, kernel, c->tmIN, c->tmX, c->tmH, p->aplanes == 3 ? c->tmXl : c->tmX,
+                                    p->aplanes == 3 ? c->tmHl : c->tmH, c->tmXo, c->tmHo,
+                                    (const dct::TowerLayer*)p->tower_table, n_layers, X, static_cast<T*>(c->H),
+                                    static_cast<int>(dc::cells_for(nb)), p->Cp, npairs, p->row_bytes() / p->elt,
+                                    p->row_bytes(), c->Qa, c->tile_flags, c->tile_flags + words, c->tile_cap,
+                                    target, c->d_err);
+        }
+        if (le == cudaSuccess) le = cudaGetLastError();
+        if (le != cudaSuccess) {
+            // e.g. cooperative launches with clusters not available: keep to a launch per layer
+            (void)cudaGetLastError();
+            p->tower_refused = true;
+        } else {
+            const int cells = nb * kSq;
+            {
+                LaunchScope scope(c, kClassHead);
+                dc::head_conv_cells_kernel<T><<<(cells + 7) / 8, 256, 0, c->stream>>>(
+                    X, p->head_w, p->Cp, cells, pol_dev, val_dev, p->row_bytes() / p->elt,
+                    (p->aplanes == 2 || (p->aplanes == 3 && p->layers.back().out_lo)) ? p->Cp : 0,
+                    p->aplanes == 3 ? 1 : 0);
+            }
+            LZB_CUDA(cudaGetLastError());
+            return LZB_OK;
+        }
+    }
     if ((rc = launch_conv_direct<T>(c, p->layers[0], nb, c->tmIN, c->tmXo, nullptr, nullptr, c->X, nullptr,
                                     layer_flags(0), layer_counts(0), target))) {
         return rc;
@@ -665,6 +721,12 @@ int set_smem_attrs() {
             LZB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, dc2::kD2SmemBytes));
         }
     }
+    LZB_CUDA(cudaFuncSetAttribute(dct::conv_tower_kernel<__half, 1>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dct::kTowerSmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dct::conv_tower_kernel<__half, 3>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dct::kTowerSmemBytes));
+    LZB_CUDA(cudaFuncSetAttribute(dct::conv_tower_kernel<__nv_bfloat16, 1>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, dct::kTowerSmemBytes));
     LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__half, 1>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, dc3::kD3SmemBytes));
     LZB_CUDA(cudaFuncSetAttribute(dc3::conv_ksplit_kernel<__half, 3>,
@@ -1118,6 +1180,7 @@ void lzb_pipe_destroy(lzb_pipe* p) {
         cudaFree(L.invstd);
     }
     cudaFree(p->head_w);
+    cudaFree(p->tower_table);
     Heads& h = p->heads;
     float* hs[] = {h.bn_pol_mean, h.bn_pol_invstd, h.ip_pol_wT, h.ip_pol_b, h.bn_val_mean,
                    h.bn_val_invstd, h.ip1_val_wT, h.ip1_val_b, h.ip2_val_w, h.ip2_val_b};
@@ -1184,6 +1247,35 @@ int lzb_pipe_finalize(lzb_pipe* p) {
         if (!p->layers[l].present) return fail(LZB_ERR_ARG, "layer " + std::to_string(l) + " missing");
     }
     if (!p->head_convs) return fail(LZB_ERR_ARG, "head convolutions missing");
+    // the one-launch tower (conv_tower.cuh): CTA pairs, one or the e5m2 two-plane form
+    if (p->direct && p->pairs && (p->aplanes == 1 || p->aplanes == 3) && p->blocks > 0) {
+        LZB_CUDA(enter_device(p->device));
+        std::vector<dct::TowerLayer> table(p->layers.size());
+        for (size_t l = 0; l < p->layers.size(); l++) {
+            const Layer& L = p->layers[l];
+            dct::TowerLayer& t = table[l];
+            std::memset(&t, 0, sizeof(t));
+            t.tmW = L.tmW2[1];
+            t.tmWl = L.Wd8 ? L.tmW8[1] : L.tmW2[1];
+            t.mean = L.mean;
+            t.invstd = L.invstd;
+            const bool second = l > 0 && l % 2 == 0;          // second convolution of a block
+            t.in_sel = l == 0 ? 0 : (second ? 2 : 1);
+            t.out_sel = (l == 0 || second) ? 1 : 2;
+            t.fchunks = L.cinw / tc::kChunkK;
+            t.kchunks = t.fchunks + L.lchunks;
+            t.achunks = L.achunks;
+            t.has_res = second ? 1 : 0;
+            // the planes a layer reads and writes, as the launch-per-layer path decides them
+            const bool planes = p->aplanes == 3 && (L.out_lo || L.lchunks > 0);
+            t.res_lo = (second && planes) ? 1 : 0;
+            t.out_lo = (planes && L.out_lo) ? 1 : 0;
+            t.out_hi8 = (planes && L.out_hi8) ? 1 : 0;
+        }
+        LZB_CUDA(cudaMalloc(&p->tower_table, table.size() * sizeof(dct::TowerLayer)));
+        LZB_CUDA(cudaMemcpy(p->tower_table, table.data(), table.size() * sizeof(dct::TowerLayer),
+                            cudaMemcpyHostToDevice));
+    }
     p->finalized = true;
     return LZB_OK;
 }
@@ -1251,6 +1343,8 @@ int lzb_ctx_create(lzb_ctx** out, lzb_pipe* p, int max_batch) {
         const char* tf = getenv("LZB_TILE_FLAGS");
         const bool tile_flags = tf != nullptr ? atoi(tf) == 1 : p->aplanes == 3;
         c->tile_flags_always = tf != nullptr && atoi(tf) == 1;
+        const char* tk = getenv("LZB_TOWER_KERNEL");
+        c->tower_kernel = tk != nullptr && atoi(tk) == 1;
         if (p->pairs && tile_flags) {
             c->tile_cap = (c->Qa + dc2::kPairM - 1) / dc2::kPairM;
             // two words per layer and tile: the run that completed it last, and the arrival counter
@@ -1640,13 +1734,14 @@ int lzb_ctx_profile_end(lzb_ctx* c, double* ms_by_class, long long* launches_by_
         float ms = 0.f;
         if (rc == LZB_OK && cudaEventElapsedTime(&ms, c->prof_events[2 * i], c->prof_events[2 * i + 1]) == cudaSuccess) {
             ms_by_class[c->prof_class[i]] += ms;
-            launches_by_class[c->prof_class[i]]++;
+            launches_by_class[c->prof_class[i]] += c->prof_layers[i];
         }
         cudaEventDestroy(c->prof_events[2 * i]);
         cudaEventDestroy(c->prof_events[2 * i + 1]);
     }
     c->prof_events.clear();
     c->prof_class.clear();
+    c->prof_layers.clear();
     return rc;
 }
 

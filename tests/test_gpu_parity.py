@@ -456,12 +456,21 @@ def test_per_tile_dependencies_give_the_same_bits(lzb, W, monkeypatch, mode):
     plain = pipe.context(256)
     monkeypatch.setenv("LZB_TILE_FLAGS", "1")
     tiled = pipe.context(256)
+    # LZB_TOWER_KERNEL=1 on top of it: all layers of a large batch in ONE
+    # cooperative launch whose CTA pairs walk the layers (conv_tower.cuh)
+    monkeypatch.setenv("LZB_TOWER_KERNEL", "1")
+    tower = pipe.context(256)
     for n in (256, 64, 200, 256, 24, 131, 256):      # 24 positions: below the range it applies to
         for _ in range(3):
-            a, b = plain.forward(x[:n]), tiled.forward(x[:n])
+            a, b, t = plain.forward(x[:n]), tiled.forward(x[:n]), tower.forward(x[:n])
             assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]), n
+            assert np.array_equal(a[0], t[0]) and np.array_equal(a[1], t[1]), n
+    before = tower.launches
+    tower.forward(x)
+    assert tower.launches - before <= 4       # input planes, the tower, the 1x1 head convolutions
     plain.close()
     tiled.close()
+    tower.close()
     pipe.close()
 
 
